@@ -32,16 +32,36 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 class PagedKVRequest:
     """Keys and values of ``num_kv_heads`` x ``head_dim`` per token, paged.
     ``window`` None: all earlier tokens stay readable; else only the last
-    ``window`` positions (the current one included)."""
+    ``window`` positions (the current one included).  ``tied_values``: the values are
+    the keys themselves, so only keys are stored (``LayerCache.v`` is ``LayerCache.k``)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    tied_values: bool = False
 
 
 @dataclass(frozen=True)
 class FixedStateRequest:
     """A per-request record of fixed ``shape`` (float32) in a state slot."""
     shape: Tuple[int, ...]
+
+
+def request_parts(request) -> Tuple[object, ...]:
+    """What a mixer asks of the cache as a tuple: a mixer may ask for nothing (None), one
+    thing, or several (a tuple: pages of keys AND a fixed-size record, for instance)."""
+    if request is None:
+        return ()
+    if isinstance(request, (tuple, list)):
+        return tuple(request)
+    return (request,)
+
+
+def paged_part(request) -> Optional[PagedKVRequest]:
+    return next((r for r in request_parts(request) if isinstance(r, PagedKVRequest)), None)
+
+
+def state_part(request) -> Optional[FixedStateRequest]:
+    return next((r for r in request_parts(request) if isinstance(r, FixedStateRequest)), None)
 
 
 class CacheError(RuntimeError):

@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..parts.base import LayerCache
-from .manager import FixedStateRequest, PagedKVRequest
+from .manager import FixedStateRequest, PagedKVRequest, paged_part, state_part
 
 
 @dataclass
@@ -34,7 +34,8 @@ def plan_groups(requests: Sequence[Optional[object]]) -> Tuple[List[GroupPlan], 
     groups: List[GroupPlan] = []
     of_layer: Dict[int, int] = {}
     for layer, req in enumerate(requests):
-        if not isinstance(req, PagedKVRequest):
+        req = paged_part(req)
+        if req is None:
             continue
         for gi, g in enumerate(groups):
             if g.request == req:
@@ -50,8 +51,8 @@ def plan_groups(requests: Sequence[Optional[object]]) -> Tuple[List[GroupPlan], 
 def bytes_per_page(groups: Sequence[GroupPlan], page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page costs when every group gets the same number of pages."""
     el = torch.empty((), dtype=dtype).element_size()
-    return sum(2 * len(g.layers) * g.request.num_kv_heads * g.request.head_dim * page_size * el
-               for g in groups)
+    return sum((1 if g.request.tied_values else 2) * len(g.layers) * g.request.num_kv_heads
+               * g.request.head_dim * page_size * el for g in groups)
 
 
 def pages_from_memory(groups, page_size, dtype, free_bytes: int, utilization: float) -> int:
@@ -83,20 +84,24 @@ class CacheStorage:
         self._buffers = []
         for gi, g in enumerate(self.groups):
             r = g.request
-            buf = torch.full((len(g.layers), 2, num_pages, r.num_kv_heads, page_size, r.head_dim),
-                             POISON if poison else 0.0, dtype=dtype, device=device)
+            buf = torch.full((len(g.layers), 1 if r.tied_values else 2, num_pages, r.num_kv_heads,
+                              page_size, r.head_dim), POISON if poison else 0.0, dtype=dtype, device=device)
             self._buffers.append(buf)
             for li, layer in enumerate(g.layers):
-                self.layer_caches[layer] = LayerCache(group=gi, k=buf[li, 0], v=buf[li, 1],
+                self.layer_caches[layer] = LayerCache(group=gi, k=buf[li, 0], v=buf[li, -1],
                                                       page_size=page_size)
         self.state_layers: List[int] = []
         for layer, req in enumerate(requests):
-            if isinstance(req, FixedStateRequest):
-                st = torch.zeros((num_state_slots,) + tuple(req.shape), dtype=torch.float32,
+            fixed = state_part(req)
+            if fixed is not None:
+                st = torch.zeros((num_state_slots,) + tuple(fixed.shape), dtype=torch.float32,
                                  device=device)
-                self.layer_caches[layer] = LayerCache(state=st, page_size=page_size)
+                if layer in self.layer_caches:           # (a mixer with pages and a record)
+                    self.layer_caches[layer].state = st
+                else:
+                    self.layer_caches[layer] = LayerCache(state=st, page_size=page_size)
                 self.state_layers.append(layer)
-            elif req is None:
+            elif layer not in self.layer_caches:
                 self.layer_caches[layer] = LayerCache(page_size=page_size)
 
     @property

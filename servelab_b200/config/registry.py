@@ -1,7 +1,7 @@
 """The one registry from an architecture's name to its model.
 
-``config.json`` names its architecture in ``architectures[0]`` (falling back to
-``model_type``).  An entry supplies the typed config class of that architecture;
+``config.json`` names its architecture in ``architectures[0]`` or, as a plain string, in
+``architecture`` (falling back to ``model_type``).  An entry supplies the typed config class of that architecture;
 the config class turns itself into a ``ModelSpec`` from which the generic
 ``CausalLM`` is built, so "the model of an architecture" is data plus the parts
 it names.  The reference has no registry: its engine hard-codes one decoder
@@ -36,6 +36,8 @@ def registered_architectures() -> Tuple[str, ...]:
 
 def resolve_architecture(cfg: Dict[str, Any]) -> str:
     archs = cfg.get("architectures") or []
+    if not archs and isinstance(cfg.get("architecture"), str):
+        archs = [cfg["architecture"]]
     if archs:
         name = archs[0]
         if name in _ARCHITECTURES:

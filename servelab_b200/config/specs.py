@@ -49,6 +49,18 @@ class RMSNormSpec(PartSpec):
     eps: float = 1e-6
 
 
+@dataclass(frozen=True)
+class DynamicTanhSpec(PartSpec):
+    """Dynamic Tanh: y = tanh(alpha * x) * w + b per element, with a learned scalar
+    ``alpha``; no mean, variance or root mean square is computed.  The three tensors are
+    named ``<prefix><weight_suffix>``, ``<prefix><bias_suffix>`` and ``<prefix><alpha_suffix>``."""
+    kind: str = "dynamic_tanh"
+    dim: int = 0
+    weight_suffix: str = ".weight"
+    bias_suffix: str = ".bias"
+    alpha_suffix: str = ".alpha"
+
+
 # -------------------------------------------------------------------- mixers
 @dataclass(frozen=True)
 class AttentionSpec(PartSpec):
@@ -76,6 +88,51 @@ class AttentionSpec(PartSpec):
     position_name: str = "rotary_emb"
 
 
+@dataclass(frozen=True)
+class ConvTalkAttentionSpec(PartSpec):
+    """Windowed grouped-query softmax attention whose positions enter through the scores
+    alone, with these steps, each a parameter of its own:
+
+    ``conv_taps``        a causal convolution over time on every channel of the projected
+                         queries and keys (1: none); the last ``conv_taps - 1`` projected rows
+                         of a request are per-request state;
+    ``tied_values``      the values are the keys as they leave the convolution (no value
+                         projection, keys stored once);
+    ``q_temp_coef/every`` queries at position p are multiplied by
+                         1 + coef * ln(floor((p + 1) / every) + 1) (coef None: not applied);
+    ``distance_bias``    r1_h * ln(1 + r2_h * (i - j)) is subtracted from the scaled score of
+                         query i and key j, with two learned numbers a head;
+    ``talking_heads``    after the softmax the heads' weights are mixed by a learned [H, H]
+                         matrix; head h applies its mixed weights to its own key/value head;
+    ``output_gate``      the concatenated heads are multiplied by sigmoid(W_g x) of the
+                         mixer's input before the output projection.
+    """
+    kind: str = "conv_talk_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None
+    scale: Optional[float] = None          # None => head_dim ** -0.5
+    conv_taps: int = 1
+    tied_values: bool = True
+    q_temp_coef: Optional[float] = None
+    q_temp_every: int = 1
+    distance_bias: bool = False
+    talking_heads: bool = False
+    output_gate: bool = False
+    # checkpoint names under the mixer's prefix
+    q_name: str = "q"
+    k_name: str = "k"
+    o_name: str = "o"
+    gate_name: str = "g"
+    conv_suffix: str = ".conv"             # the taps of a projection: <projection><conv_suffix>
+    bias_r1_name: str = "r1"
+    bias_r2_name: str = "r2"
+    talk_name: str = "talk"
+    weight_suffix: str = ""
+
+
 # -------------------------------------------------------------- feed-forward
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
@@ -88,23 +145,31 @@ class GatedMLPSpec(PartSpec):
     gate_name: str = "gate_proj"           # checkpoint names under the feed-forward's prefix
     up_name: str = "up_proj"
     down_name: str = "down_proj"
+    weight_suffix: str = ".weight"         # a matrix is <prefix>.<name><weight_suffix>
 
 
 # --------------------------------------------------------------------- block
 @dataclass(frozen=True)
 class BlockSpec(PartSpec):
     """One layer: how a mixer, a feed-forward and their norms are arranged.
-    ``pre_norm`` is x += mixer(norm1(x)); x += ff(norm2(x))."""
+    ``pre_norm`` is x += mixer(norm1(x)); x += ff(norm2(x)).
+    ``sandwich_norm`` norms each sublayer's result as well before it is added:
+    x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))); its ``feed_forward`` may be
+    None (a layer that has a mixer only)."""
     kind: str = "pre_norm"
     mixer: PartSpec = None
     feed_forward: PartSpec = None
     mixer_norm: PartSpec = None
     ff_norm: PartSpec = None
-    # checkpoint names of the four parts under the layer's prefix
+    mixer_post_norm: PartSpec = None       # (sandwich_norm)
+    ff_post_norm: PartSpec = None
+    # checkpoint names of the parts under the layer's prefix
     mixer_norm_name: str = "input_layernorm"
     mixer_name: str = "self_attn"
     ff_norm_name: str = "post_attention_layernorm"
     feed_forward_name: str = "mlp"
+    mixer_post_norm_name: str = "post_mixer_norm"
+    ff_post_norm_name: str = "post_ff_norm"
 
 
 @dataclass(frozen=True)

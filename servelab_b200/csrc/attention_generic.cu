@@ -18,6 +18,16 @@
 // a window w > 0, a - r < w.  The position of local token i of a request is
 // ctx_len - q_len + i.
 //
+// Two optional steps for mixers whose scores and weights are modified:
+//   * a distance bias: r1_h * ln(1 + r2_h * (a - r)) is subtracted from the scaled score
+//     (bias_r1 / bias_r2 hold a pair of numbers per query head; null: none);
+//   * every (query head, value head) pair (`pair_out` not null): the grid's z index names the
+//     kv head whose VALUES the softmax weights of this block's query heads are applied to,
+//     and the result goes, in float32, to pair_out[token][query head][value head][D].  A
+//     mixer that mixes the heads' weights after the softmax needs exactly these: mixing the
+//     weights and then applying them to a head's values equals mixing these results
+//     (slb_mix_heads_gate below).
+//
 // Reference analogue: the per-sequence torch loop (servelab/parallel/
 // tp_model.py:136-157): gather rows by block table, repeat_interleave for the
 // groups, float32 scores * D^-1/2, causal mask, float32 softmax, float32 P.V.
@@ -38,7 +48,9 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
     T* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
-    int H, int Hkv, int D, int ps, int num_pages, float scale, int window) {
+    int H, int Hkv, int D, int ps, int num_pages, float scale, int window,
+    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2,
+    float* __restrict__ pair_out) {
     extern __shared__ float smem[];
     pdl_wait();
     const int ldd = D + 1;
@@ -49,6 +61,7 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
 
     const int tid = threadIdx.x;
     const int kvh = blockIdx.y;
+    const int vh = pair_out != nullptr ? blockIdx.z : kvh;     // the kv head whose values are used
     const int s = tile_seq[blockIdx.x];
     const int row0 = tile_row0[blockIdx.x];
     const int g = H / Hkv;
@@ -73,6 +86,12 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
     const int r = tid >> 3, c0 = tid & 7;
     const bool row_valid = r < nrows;
     const int my_pos = row_valid ? pos_base + (row0 + r) / g : -1;
+    float r1 = 0.f, r2 = 0.f;
+    if (bias_r1 != nullptr && row_valid) {
+        const int head = kvh * g + (row0 + r) % g;
+        r1 = bias_r1[head];
+        r2 = bias_r2[head];
+    }
     const int p_first = pos_base + row0 / g;
     const int p_last = pos_base + (row0 + nrows - 1) / g;
     int kbeg = 0;
@@ -97,9 +116,9 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
                 if (page >= num_pages) {
                     atomicCAS(&generic_attention_status_word, 0, 1);
                 } else if (page >= 0) {
-                    const size_t off = (((size_t)page * Hkv + kvh) * ps + kp % ps) * D + d;
-                    kv = to_float(kc[off]);
-                    vv = to_float(vc[off]);
+                    const size_t slot = (size_t)page * Hkv * ps + kp % ps;
+                    kv = to_float(kc[(slot + (size_t)kvh * ps) * D + d]);
+                    vv = to_float(vc[(slot + (size_t)vh * ps) * D + d]);
                 }
             }
             Ks[kr * ldd + d] = kv;
@@ -118,7 +137,8 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
         for (int j = 0; j < 4; ++j) {
             const int kp = k0 + c0 + 8 * j;
             const bool vis = row_valid && kp <= my_pos && (window <= 0 || my_pos - kp < window);
-            sc[j] = vis ? sc[j] * scale : -INFINITY;
+            sc[j] = vis ? sc[j] * scale - (bias_r1 != nullptr ? r1 * logf(1.f + r2 * (float)(my_pos - kp)) : 0.f)
+                        : -INFINITY;
             tmax = fmaxf(tmax, sc[j]);
         }
         tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -160,6 +180,15 @@ __global__ void __launch_bounds__(AG_THREADS) paged_attention_generic_kernel(
         const int rho = row0 + r;
         const int tl = rho / g, hg = rho - tl * g;
         const float inv = l > 0.f ? 1.0f / l : 0.f;
+        if (pair_out != nullptr) {
+            float* o = pair_out + (((size_t)(q0 + tl) * H + (size_t)(kvh * g + hg)) * Hkv + vh) * D;
+#pragma unroll
+            for (int j = 0; j < AG_MAX_D / 8; ++j) {
+                const int c = c0 + 8 * j;
+                if (j < nj && c < D) o[c] = acc[j] * inv;
+            }
+            return;
+        }
         T* o = out + (size_t)(q0 + tl) * ldo + (size_t)(kvh * g + hg) * D;
 #pragma unroll
         for (int j = 0; j < AG_MAX_D / 8; ++j) {
@@ -174,10 +203,12 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
                           const int* block_table, int max_pages, const int* cu_q,
                           const int* ctx_len, const int* tile_seq, const int* tile_row0,
                           int num_tiles, int H, int Hkv, int D, int ps, int num_pages, float scale,
-                          int window, cudaStream_t st) {
+                          int window, const float* bias_r1, const float* bias_r2, float* pair_out,
+                          cudaStream_t st) {
     if (num_tiles <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0)
         return SLB_ERR_BAD_ARG;
+    if ((bias_r1 == nullptr) != (bias_r2 == nullptr)) return SLB_ERR_BAD_ARG;
     if (D > AG_MAX_D || Hkv > 65535) return SLB_ERR_TOO_LARGE;
     const size_t smem = ((size_t)(AG_BM + 2 * AG_BN) * (D + 1) + AG_BM * (AG_BN + 1)) * sizeof(float);
     // the largest this kernel can ask for (head size AG_MAX_D), set once per device
@@ -185,9 +216,50 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
     static unsigned long long configured = 0;     // per template instance, a bit per device
     const int rc = slb_configure(&configured, paged_attention_generic_kernel<T>, SMEM_MAX);
     if (rc != 0) return rc;
-    return slb_launch(paged_attention_generic_kernel<T>, dim3(num_tiles, Hkv), dim3(AG_THREADS), smem,
-                      st, q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, D, ps, num_pages, scale, window);
+    return slb_launch(paged_attention_generic_kernel<T>, dim3(num_tiles, Hkv, pair_out != nullptr ? Hkv : 1),
+                      dim3(AG_THREADS), smem, st, q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q,
+                      ctx_len, tile_seq, tile_row0, H, Hkv, D, ps, num_pages, scale, window, bias_r1,
+                      bias_r2, pair_out);
+}
+
+// What follows the attention of a mixer with mixed heads and an output gate, in one pass:
+//   out[t][h][d] = (sum_g talk[h][g] * pairs[t][g][kv(h)][d]) * sigmoid(gate[t][h][d])
+// `pairs` (float32, from the kernel above) may be null: then `direct` [T, H D] (type T) is the
+// attention's plain result and only the gate is applied; `talk` and `gate` may each be null.
+template <typename T>
+__global__ void __launch_bounds__(256) mix_heads_gate_kernel(
+    const float* __restrict__ pairs, const T* __restrict__ direct, int ldi,
+    const float* __restrict__ talk, const T* __restrict__ gate, int ldg, T* __restrict__ out, int ldo,
+    int H, int Hkv, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= H * D) return;
+    const int h = idx / D, d = idx - h * D;
+    float v;
+    if (pairs != nullptr) {
+        const int vh = h / (H / Hkv);
+        const float* p = pairs + (((size_t)t * H) * Hkv + vh) * D + d;
+        v = 0.f;
+        for (int g = 0; g < H; ++g)
+            v += (talk != nullptr ? talk[h * H + g] : (g == h ? 1.f : 0.f)) * p[(size_t)g * Hkv * D];
+    } else {
+        v = to_float(direct[(size_t)t * ldi + idx]);
+    }
+    if (gate != nullptr) v *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * ldg + idx])));
+    out[(size_t)t * ldo + idx] = from_float<T>(v);
+}
+
+template <typename T>
+static int launch_mix(const float* pairs, const T* direct, int ldi, const float* talk, const T* gate,
+                      int ldg, T* out, int ldo, int T_tokens, int H, int Hkv, int D, cudaStream_t st) {
+    if (T_tokens <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || T_tokens > 65535 ||
+        (pairs == nullptr) == (direct == nullptr))
+        return SLB_ERR_BAD_ARG;
+    return slb_launch(mix_heads_gate_kernel<T>, dim3((H * D + 255) / 256, T_tokens), dim3(256), 0, st,
+                      pairs, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
 }
 
 extern "C" {
@@ -195,17 +267,31 @@ int slb_paged_attention_generic_f32(const float* q, int ldq, const float* kc, co
                                     float* out, int ldo, const int* block_table, int max_pages,
                                     const int* cu_q, const int* ctx_len, const int* tile_seq,
                                     const int* tile_row0, int num_tiles, int H, int Hkv, int D,
-                                    int ps, int num_pages, float scale, int window, cudaStream_t st) {
+                                    int ps, int num_pages, float scale, int window, const float* bias_r1,
+        const float* bias_r2, float* pair_out, cudaStream_t st) {
     return launch_generic<float>(q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len,
-                                 tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window, st);
+                                 tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window,
+                                 bias_r1, bias_r2, pair_out, st);
 }
 int slb_paged_attention_generic_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
                                      bf16* out, int ldo, const int* block_table, int max_pages,
                                      const int* cu_q, const int* ctx_len, const int* tile_seq,
                                      const int* tile_row0, int num_tiles, int H, int Hkv, int D,
-                                     int ps, int num_pages, float scale, int window, cudaStream_t st) {
+                                     int ps, int num_pages, float scale, int window, const float* bias_r1,
+        const float* bias_r2, float* pair_out, cudaStream_t st) {
     return launch_generic<bf16>(q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len,
-                                tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window, st);
+                                 tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window,
+                                 bias_r1, bias_r2, pair_out, st);
+}
+int slb_mix_heads_gate_f32(const float* pairs, const float* direct, int ldi, const float* talk,
+                           const float* gate, int ldg, float* out, int ldo, int T_tokens, int H, int Hkv,
+                           int D, cudaStream_t st) {
+    return launch_mix<float>(pairs, direct, ldi, talk, gate, ldg, out, ldo, T_tokens, H, Hkv, D, st);
+}
+int slb_mix_heads_gate_bf16(const float* pairs, const bf16* direct, int ldi, const float* talk,
+                            const bf16* gate, int ldg, bf16* out, int ldo, int T_tokens, int H, int Hkv,
+                            int D, cudaStream_t st) {
+    return launch_mix<bf16>(pairs, direct, ldi, talk, gate, ldg, out, ldo, T_tokens, H, Hkv, D, st);
 }
 // rows per tile of the generic kernel (the host builds the tile list with it)
 int slb_paged_attention_generic_tile_rows() { return AG_BM; }

@@ -47,3 +47,29 @@ def paged_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, 
                                 scale, window)
             return
     _generic(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale, window)
+
+
+# ---------------------------------------------- attention with mixed heads
+def prepare_talk_attention(head_dim: int, dtype: torch.dtype) -> None:
+    """Builds what ``talk_attention`` will launch for this head size (at load, not in a step)."""
+
+
+def talk_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale, window,
+                   bias_r1, bias_r2, talk, gate) -> None:
+    """Windowed attention with a log-distance bias, then the heads' softmax weights mixed by
+    ``talk`` [H, H] (None: not mixed) and the result multiplied by sigmoid(``gate``) (None:
+    not gated), into ``out`` [T, H D].  Mixed heads go through the results of every (query
+    head, kv head) pair, float32 [T, H, Hkv, D], which ``mix_heads_gate`` combines."""
+    T = q.shape[0]
+    g = H // Hkv
+    tile_seq, tile_row0, n = ctx.attention_tiles(g, K.generic_attention_tile_rows())
+    if talk is None:
+        K.paged_attention_generic(q, k_cache, v_cache, out, table, ctx.cu_q, ctx.ctx_len, tile_seq,
+                                  tile_row0, n, H, Hkv, D, page_size, scale, window, bias_r1, bias_r2)
+        if gate is not None:
+            K.mix_heads_gate(None, out, None, gate, out, H, Hkv, D)
+        return
+    pairs = torch.empty((T, H, Hkv, D), dtype=torch.float32, device=q.device)
+    K.paged_attention_generic(q, k_cache, v_cache, None, table, ctx.cu_q, ctx.ctx_len, tile_seq,
+                              tile_row0, n, H, Hkv, D, page_size, scale, window, bias_r1, bias_r2, pairs)
+    K.mix_heads_gate(pairs, None, talk, gate, out, H, Hkv, D)

@@ -232,13 +232,75 @@ def generic_attention_tile_rows() -> int:
 
 def paged_attention_generic(q, k_cache, v_cache, out, block_table, cu_q, ctx_len, tile_seq,
                             tile_row0, num_tiles: int, num_heads: int, num_kv_heads: int,
-                            head_dim: int, page_size: int, scale: float, window: int) -> None:
+                            head_dim: int, page_size: int, scale: float, window: int,
+                            bias_r1: Optional[torch.Tensor] = None,
+                            bias_r2: Optional[torch.Tensor] = None,
+                            pair_out: Optional[torch.Tensor] = None) -> None:
+    """``bias_r1`` / ``bias_r2`` (float32 [H]): r1_h ln(1 + r2_h distance) is subtracted from the
+    scaled scores.  ``pair_out`` (float32 [T, H, Hkv, D]): instead of ``out`` (may be None then)
+    the result of every query head's weights applied to every kv head's values."""
     fn = getattr(L.core(), "slb_paged_attention_generic_" + _suffix(q.dtype))
-    L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-               out.stride(0), block_table.data_ptr(), block_table.shape[1], cu_q.data_ptr(),
-               ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), num_tiles,
+    L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), _p(out),
+               out.stride(0) if out is not None else 0, block_table.data_ptr(), block_table.shape[1],
+               cu_q.data_ptr(), ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), num_tiles,
                num_heads, num_kv_heads, head_dim, page_size, k_cache.shape[0], float(scale),
-               int(window), _stream()), "paged_attention_generic")
+               int(window), _p(bias_r1), _p(bias_r2), _p(pair_out), _stream()), "paged_attention_generic")
+
+
+def mix_heads_gate(pairs: Optional[torch.Tensor], direct: Optional[torch.Tensor],
+                   talk: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
+                   num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """out[t, h] = (sum_g talk[h, g] pairs[t, g, kv(h)]) * sigmoid(gate[t, h]); with ``pairs``
+    None, ``direct`` [T, H D] takes the place of the sum.  ``gate`` [T, H D] may be a view of
+    a wider projection (its row stride is passed); ``talk`` float32 [H, H]."""
+    fn = getattr(L.core(), "slb_mix_heads_gate_" + _suffix(out.dtype))
+    L.check(fn(_p(pairs), _p(direct), direct.stride(0) if direct is not None else 0, _p(talk),
+               _p(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0),
+               out.shape[0], num_heads, num_kv_heads, head_dim, _stream()), "mix_heads_gate")
+
+
+def dyt_add_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], post, pre,
+                 out: Optional[torch.Tensor], row_map: Optional[torch.Tensor] = None) -> None:
+    """Dynamic Tanh around a residual add.  ``post`` / ``pre`` are (alpha, weight, bias)
+    float32 device tensors or None.  d = post(delta) (or delta); resid += d in place (not when
+    ``row_map`` selects rows); out[r] = pre(resid[src(r)] + d)."""
+    dtype = out.dtype if out is not None else delta.dtype
+    rows = out.shape[0] if out is not None else resid.shape[0]
+    pa, pw, pb = post if post is not None else (None, None, None)
+    a, w, b = pre if pre is not None else (None, None, None)
+    fn = getattr(L.core(), "slb_dyt_add_norm_" + _suffix(dtype))
+    L.check(fn(resid.data_ptr(), resid.stride(0), _p(delta), delta.stride(0) if delta is not None else 0,
+               _p(pa), _p(pw), _p(pb), _p(a), _p(w), _p(b), _p(out),
+               out.stride(0) if out is not None else 0, _p(row_map), rows, resid.shape[1], _stream()),
+            "dyt_add_norm")
+
+
+def qk_conv_cache(proj: torch.Tensor, taps_w: torch.Tensor, state: Optional[torch.Tensor], ctx,
+                  block_table: torch.Tensor, page_size: int, temp_coef: float, temp_every: int,
+                  q_out: torch.Tensor, k_cache: Optional[torch.Tensor], num_kv_heads: int,
+                  head_dim: int) -> None:
+    """Causal convolution over time (``taps_w`` float32 [C, taps]) on the first C = q width +
+    kv width columns of ``proj``, with the rows before a portion taken from ``state``
+    (float32 [slots, taps - 1, C], indexed by ``ctx.state_slots`` and updated); queries times
+    their temperature into ``q_out``, keys into the pages of ``k_cache`` (None: not written)."""
+    fn = getattr(L.core(), "slb_qk_conv_cache_" + _suffix(proj.dtype))
+    n = 1 if (taps_w.shape[1] == 1 or ctx.decode_only) else 2
+    L.check(fn(proj.data_ptr(), proj.stride(0), taps_w.data_ptr(), taps_w.shape[1], _p(state),
+               ctx.state_slots.data_ptr(), ctx.cu_q.data_ptr(), ctx.seq_of_token.data_ptr(),
+               ctx.positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+               _num_pages(k_cache), float(temp_coef), int(temp_every), q_out.data_ptr(), q_out.stride(0),
+               _p(k_cache), proj.shape[0], ctx.num_seqs, q_out.shape[1], num_kv_heads, head_dim,
+               1 if ctx.decode_only else 0, _stream()), "qk_conv_cache")
+    global launch_count
+    launch_count += n - 1
+
+
+CONV_MAX_TAPS = 16             # taps of the short convolution the kernel holds in registers
+
+
+def conv_cache_status(reset: bool = False) -> int:
+    """0 unless the convolution kernel met a block-table entry outside the cache."""
+    return L.core().slb_conv_cache_status(1 if reset else 0)
 
 
 # ---------------------------------------------------------- matrix products

@@ -35,8 +35,15 @@ _CORE_SIGNATURES = {
     "slb_qkv_rope_cache_f32": [P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_qkv_rope_cache_bf16": [P, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_cache_write_status": [I],
-    "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
-    "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P],
+    "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P],
+    "slb_mix_heads_gate_f32": [P, P, I, P, P, I, P, I, I, I, I, I, P],
+    "slb_mix_heads_gate_bf16": [P, P, I, P, P, I, P, I, I, I, I, I, P],
+    "slb_dyt_add_norm_f32": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
+    "slb_dyt_add_norm_bf16": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
+    "slb_qk_conv_cache_f32": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, P],
+    "slb_qk_conv_cache_bf16": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, P],
+    "slb_conv_cache_status": [I],
     "slb_paged_attention_generic_status": [I],
     "slb_paged_attention_generic_tile_rows": [],
     "slb_gemm_simt_f32": [P, I, P, I, P, I, P, I, I, I, P],

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from ..ops.kernels import plain_unless
 from .base import Block
+from .norm import PostNormed
 from .registry import FEED_FORWARDS, MIXERS, NORMS, build_part, part_class, register_block
 
 
@@ -62,3 +63,55 @@ class PreNormBlock(Block):
         a = self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache)
         x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
         return resid, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x))
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(PreNormBlock):
+    """x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))): each sublayer's result passes
+    a norm of its own before it is added.  The result travels to the next norm kernel as a
+    ``PostNormed`` value, so norm-of-result, add and norm-of-next-input are one launch where
+    the norms' kind allows.  ``feed_forward`` None: the layer ends after the mixer."""
+
+    @staticmethod
+    def _members(spec, prefix):
+        out = [(NORMS, spec.mixer_norm, f"{prefix}.{spec.mixer_norm_name}"),
+               (MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}"),
+               (NORMS, spec.mixer_post_norm, f"{prefix}.{spec.mixer_post_norm_name}")]
+        if spec.feed_forward is not None:
+            out += [(NORMS, spec.ff_norm, f"{prefix}.{spec.ff_norm_name}"),
+                    (FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}"),
+                    (NORMS, spec.ff_post_norm, f"{prefix}.{spec.ff_post_norm_name}")]
+        return tuple(out)
+
+    def _build(self, spec, prefix, env):
+        parts = [build_part(table, part, name, env) for table, part, name in self._members(spec, prefix)]
+        self.mixer_norm, self.mixer, self.mixer_post_norm = parts[:3]
+        self.ff_norm, self.feed_forward, self.ff_post_norm = (parts[3:] if len(parts) > 3
+                                                              else (None, None, None))
+        self._parts = parts
+
+    def __init__(self, spec, prefix, env):
+        Block.__init__(self, spec, prefix, env)
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and
+                                            (spec.ff_norm is None or spec.ff_post_norm is None)):
+            raise ValueError("sandwich_norm: every sublayer needs a norm before and after it")
+        self._build(spec, prefix, env)
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self._parts)
+
+    def load(self, store):
+        for p in self._parts:
+            p.load(store)
+
+    accepts_split_sum = False
+    accepts_deferred_linear = False
+    accepts_post_normed = True        # the incoming ``delta`` may be a PostNormed value
+
+    def forward(self, ctx, resid, delta, cache, owns_cache):
+        x = self.mixer_norm.forward(ctx, resid, plain_unless(self.mixer_norm, delta))
+        a = plain_unless(None, self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache))
+        a = PostNormed(ctx, a, self.mixer_post_norm)
+        if self.feed_forward is None:
+            return resid, a
+        x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
+        f = plain_unless(None, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x)))
+        return resid, PostNormed(ctx, f, self.ff_post_norm)

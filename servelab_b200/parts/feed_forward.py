@@ -31,13 +31,15 @@ class GatedMLP(FeedForward):
     @classmethod
     def declare(cls, spec, prefix):
         h, i = spec.hidden_size, spec.intermediate_size
-        return [TensorDecl(f"{prefix}.{spec.gate_name}.weight", (i, h), MATRIX),
-                TensorDecl(f"{prefix}.{spec.up_name}.weight", (i, h), MATRIX),
-                TensorDecl(f"{prefix}.{spec.down_name}.weight", (h, i), MATRIX)]
+        sfx = spec.weight_suffix
+        return [TensorDecl(f"{prefix}.{spec.gate_name}{sfx}", (i, h), MATRIX),
+                TensorDecl(f"{prefix}.{spec.up_name}{sfx}", (i, h), MATRIX),
+                TensorDecl(f"{prefix}.{spec.down_name}{sfx}", (h, i), MATRIX)]
 
     def load(self, store):
-        gate = store.get(f"{self.prefix}.{self.spec.gate_name}.weight")
-        up = store.get(f"{self.prefix}.{self.spec.up_name}.weight")
+        sfx = self.spec.weight_suffix
+        gate = store.get(f"{self.prefix}.{self.spec.gate_name}{sfx}")
+        up = store.get(f"{self.prefix}.{self.spec.up_name}{sfx}")
         inter, h = gate.shape
         self.block = K.SWIGLU_BLOCK if inter % K.SWIGLU_BLOCK == 0 else 0
         if self.block:
@@ -46,7 +48,7 @@ class GatedMLP(FeedForward):
                                          dim=1).reshape(2 * inter, h).contiguous()
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0)
-        self.w_down = store.get(f"{self.prefix}.{self.spec.down_name}.weight")
+        self.w_down = store.get(f"{self.prefix}.{self.spec.down_name}{sfx}")
 
     def forward(self, ctx, x):
         act = gated_linear(x, self.w_gate_up, self.block)

@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual add that precedes it.
+"""Norms fused with the residual add that precedes them: RMSNorm and Dynamic Tanh.
 
 y = x * rsqrt(mean(x^2) + eps) * w in float32 (tests/test_triton_kernels.py:57-59,
 servelab/attention/triton/paged_attention.py:76-91 in the reference); the weight
@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from ..weights.source import NORM, TensorDecl
+from ..weights.source import BIAS, NORM, TensorDecl
 from .base import Norm
 from .registry import register_norm
 
@@ -39,3 +39,67 @@ class RMSNorm(Norm):
         out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, out_rows)
         return out
+
+
+class PostNormed:
+    """A sublayer's result that still lacks the norm it must pass before it is added to the
+    stream (the "b" norm of a sandwich block): the next norm kernel applies that norm, the add
+    and itself in one pass if it is of a kind that can (``accepts_post_normed``); otherwise
+    ``materialize()`` runs the norm on the result alone."""
+
+    accept_flag = "accepts_post_normed"
+
+    def __init__(self, ctx, value: torch.Tensor, norm: "Norm"):
+        self.ctx, self.value, self.norm = ctx, value, norm
+
+    @property
+    def shape(self):
+        return self.value.shape
+
+    def materialize(self) -> torch.Tensor:
+        return self.norm.apply(self.ctx, self.value)
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha x) w + b, float32 arithmetic, nothing reduced over the row.  Being
+    elementwise it also takes a ``PostNormed`` update whose pending norm is a Dynamic Tanh:
+    one kernel then norms the update, adds it and norms the sum."""
+    graph_safe = True
+    accepts_post_normed = True
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), NORM),
+                TensorDecl(prefix + spec.bias_suffix, (spec.dim,), BIAS),
+                TensorDecl(prefix + spec.alpha_suffix, (), BIAS)]
+
+    def load(self, store):
+        s = self.spec
+        self.weight = store.get(self.prefix + s.weight_suffix)
+        self.bias = store.get(self.prefix + s.bias_suffix)
+        self.alpha = store.get(self.prefix + s.alpha_suffix).reshape(1)
+        self.params = (self.alpha, self.weight, self.bias)
+
+    def forward(self, ctx, resid, delta, out_rows=None):
+        post = None
+        if isinstance(delta, PostNormed):
+            if isinstance(delta.norm, DynamicTanh):
+                post, delta = delta.norm.params, delta.value
+            else:
+                delta = delta.materialize()
+        rows = resid.shape[0] if out_rows is None else out_rows.numel()
+        out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
+        K.dyt_add_norm(resid, delta, post, self.params, out, out_rows)
+        return out
+
+    def apply(self, ctx, x):
+        """The norm of ``x`` [T, dim] alone (no stream, no add), in the compute dtype."""
+        stream = x.to(torch.float32)
+        out = torch.empty((x.shape[0], self.spec.dim), dtype=self.env.dtype, device=x.device)
+        K.dyt_add_norm(stream, None, None, self.params, out, None)
+        return out
+
+    def add_into(self, ctx, resid, delta) -> None:
+        """resid += this norm of ``delta`` (the close of a branch that nothing norms after)."""
+        K.dyt_add_norm(resid, delta, self.params, None, None, None)

@@ -29,7 +29,7 @@ class TraceSession:
     tokens each live request holds.  ``run_step`` executes one trace step."""
 
     def __init__(self, model: str, dtype: str, max_tokens: int, page_size: int = 16,
-                 max_live: int = 8, poison_cache: bool = False, cuda_graphs: bool = False,
+                 max_live: int = 4, poison_cache: bool = False, cuda_graphs: bool = False,
                  runner=None):
         """``model``: a model folder; or hand in a ``runner`` built elsewhere (a typed config
         with weights made on the device).  ``poison_cache`` and ``cuda_graphs`` are what
@@ -89,7 +89,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-live", type=int, default=8, help="state slots (live requests)")
+    ap.add_argument("--max-live", type=int, default=4, help="state slots (live requests)")
     args = ap.parse_args(argv)
 
     print("[trace_run] loading (kernels are compiled at first use)", file=sys.stderr, flush=True)
