@@ -1,0 +1,153 @@
+"""Prefill and decode throughput of the Dezelorn design beside the Qwen2 decoder at equal layer
+sizes (random weights), with the attention kernels' own times and roofline fractions.
+
+Both models get the same width, heads, kv heads, head size, feed-forward size, layer count,
+vocabulary and sliding window, so the matrix products do nearly the same work (Dezelorn has a
+gate projection instead of a value projection) and what differs is the mixer: a convolution
+on q and k, keys that are also the values (half the cache bytes), the distance bias, and the
+heads mixed after the softmax -- which this package computes as one attention result per
+(query head, kv head) pair, so its attention does kv_heads times the arithmetic of the plain
+one.  ``python bench.py --compare dezelorn`` prints one JSON line with, per size and model:
+prefill tokens per second (one 2,048-token prompt), decode tokens per second at batch 8 and 64
+(contexts of 1,536 tokens, graphs), and per-kernel microseconds of an eager prefill and an
+eager decode step of 8 requests.
+"""
+
+from __future__ import annotations
+
+from typing import Dict
+
+PROMPT, CONTEXT, PAGE, WINDOW, LAYERS, VOCAB = 2048, 1536, 16, 1024, 4, 32000
+SIZES = {                       # width, heads, kv heads, head size, feed-forward
+    "1b-like": (2048, 16, 4, 128, 5632),
+    "3b-like": (2048, 16, 2, 128, 11008),
+    "7b-like": (3584, 28, 4, 128, 18944),
+    "small-heads": (1536, 24, 4, 64, 4096),
+}
+
+
+def dezelorn_config(width, heads, kv, dim, ff, layers=LAYERS) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "conv": 4, "scale": dim ** -0.5,
+             "mask": {"size": WINDOW}, "q_temp": {"coef": 0.3, "every": 128}}
+    return {"architecture": "Dezelorn", "vocab": VOCAB, "width": width, "embedding": {"scale": 8.0},
+            "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}
+                       for _ in range(layers)]}
+
+
+def qwen2_config(width, heads, kv, dim, ff, layers=LAYERS) -> dict:
+    from .workloads import QWEN2
+    return dict(QWEN2, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv, head_dim=dim, intermediate_size=ff, vocab_size=VOCAB,
+                tie_word_embeddings=False, use_sliding_window=True, sliding_window=WINDOW,
+                max_window_layers=0)
+
+
+def _measure(cfg: dict, note) -> Dict[str, object]:
+    import torch
+    from ..ops import kernels as K
+    from ..ops.profile import StepProfile
+    from . import workloads as W
+    pages = 64 * (-(-(CONTEXT + 64) // PAGE)) + PROMPT // PAGE + 8
+    engine = W.make_engine(cfg, pages, 64, PROMPT, 4096, weights_seed=3, page_size=PAGE)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(2)
+    vocab = runner.spec.vocab_size
+    out: Dict[str, object] = {}
+
+    def timed(fn, repeats, warmup):
+        for _ in range(warmup):
+            fn()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeats):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / repeats
+
+    # prefill: one prompt, whole, through the step function
+    ids = torch.randint(0, vocab, (PROMPT,), generator=gen).tolist()
+    runner.cache.open("p")
+    runner.cache.ensure("p", PROMPT)
+    entry = runner.entry("p", ids, 0, (PROMPT - 1,))
+    saved = runner.cuda_graphs
+    runner.cuda_graphs = False                    # (a step with a state record runs eagerly anyway)
+    ms = timed(lambda: runner.step([entry]), 5, 3)
+    out["prefill_ms"] = round(ms, 3)
+    out["prefill_tok_s"] = round(PROMPT / (ms * 1e-3), 1)
+    with StepProfile() as prof:
+        runner.step([entry])
+    out["prefill_kernels_us"] = prof.summary(1)
+    runner.cuda_graphs = saved
+    runner.cache.release("p")
+
+    # decode: requests that hold CONTEXT tokens (pages taken, not prefilled: a step's time does
+    # not depend on the values in the cache)
+    for batch in (8, 64):
+        rids = [f"d{batch}-{i}" for i in range(batch)]
+        for rid in rids:
+            assert runner.cache.open(rid) and runner.cache.ensure(rid, CONTEXT)
+            runner.cache.trim(rid, CONTEXT - 1)
+        entries = [runner.entry(rid, [1 + i], CONTEXT - 1, (0,)) for i, rid in enumerate(rids)]
+        tok = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+        ms = timed(lambda: K.sample_rows(runner.step(entries), tok), 50, 10)
+        out[f"decode_b{batch}_ms"] = round(ms, 4)
+        out[f"decode_b{batch}_tok_s"] = round(batch / (ms * 1e-3), 1)
+        if batch == 8:
+            runner.cuda_graphs = False
+            runner.step(entries)
+            with StepProfile() as prof:
+                for _ in range(5):
+                    runner.step(entries)
+            out["decode_b8_kernels_us"] = prof.summary(5)
+            runner.cuda_graphs = saved
+        for rid in rids:
+            runner.cache.release(rid)
+    del engine, runner
+    torch.cuda.empty_cache()
+    return out
+
+
+def _attention_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[str, object]:
+    """Achieved fractions of the measured peaks for the attention kernels of both models, per
+    layer.  Decode: bytes of the visible keys (and values, where they are stored) of 8 requests
+    over the kernel's time, of the copy bandwidth.  Prefill: 4 T W' H D flops (scores and
+    weighted values of the visible pairs; W' the mean number of visible keys) over the kernel's
+    time, of the bf16 peak -- the same count for both, so that the fraction says how far each
+    is from the arithmetic the design needs, not from what the kernel happens to do."""
+    width, heads, kv, dim, ff = SIZES[size]
+    seen = min(CONTEXT, WINDOW)
+    pairs = sum(min(t + 1, WINDOW) for t in range(PROMPT))
+    flops = 4.0 * pairs * heads * dim
+    out = {}
+    for arch, stored, names in (("dezelorn", 1, ("talk_decode_attention", "talk_prefill_attention")),
+                                ("qwen2", 2, ("decode_attention", "prefill_attention_tc"))):
+        dec = res[arch]["decode_b8_kernels_us"].get(names[0])
+        pre = res[arch]["prefill_kernels_us"].get(names[1]) or res[arch]["prefill_kernels_us"].get("prefill_attention")
+        nbytes = 8 * seen * kv * dim * 2 * stored
+        if dec:
+            out[f"{arch}_decode_attention_us"] = round(dec / LAYERS, 2)
+            out[f"{arch}_decode_attention_hbm_frac"] = round(nbytes / (dec / LAYERS * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+        if pre:
+            out[f"{arch}_prefill_attention_us"] = round(pre / LAYERS, 1)
+            out[f"{arch}_prefill_attention_bf16_frac"] = round(flops / (pre / LAYERS * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+    return out
+
+
+def run(peaks, note=lambda m: None, sizes=None) -> Dict[str, object]:
+    result = {"compare": "dezelorn vs qwen2 at equal layer sizes", "layers": LAYERS, "prompt": PROMPT,
+              "decode_context": CONTEXT, "window": WINDOW, "vocab": VOCAB, "dtype": "bf16",
+              "data": "synthetic: random weights, token ids uniform over the vocabulary",
+              "peaks": peaks.get("source"), "sizes": {}}
+    for size in (sizes or SIZES):
+        dims = SIZES[size]
+        res = {}
+        for arch, make in (("dezelorn", dezelorn_config), ("qwen2", qwen2_config)):
+            note(f"{size}: {arch}")
+            res[arch] = _measure(make(*dims), note)
+        res["attention"] = _attention_rooflines(size, res, peaks)
+        res["dims"] = dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), dims))
+        result["sizes"][size] = res
+    return result

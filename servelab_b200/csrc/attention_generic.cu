@@ -223,27 +223,56 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
 }
 
 // What follows the attention of a mixer with mixed heads and an output gate, in one pass:
-//   out[t][h][d] = (sum_g talk[h][g] * pairs[t][g][kv(h)][d]) * sigmoid(gate[t][h][d])
-// `pairs` (float32, from the kernel above) may be null: then `direct` [T, H D] (type T) is the
+//   out[t][h][d] = (sum_g talk[h][g] * pairs[t][g][c(h)][d]) * sigmoid(gate[t][h][d])
+// `pairs` (float32) holds, per query head g, its softmax weights applied to the values of
+// nvh kv heads: nvh = Hkv (every pair; c(h) is h's kv head) or 1 (each head's own kv head only,
+// which is all an unmixed mixer needs; talk must then be null).  With `pair_ml` the pairs are
+// the unnormalised partials of `splits` key ranges, pairs[t][g][c][split][d], with their running
+// maxima (base-2 domain) and sums in pair_ml[t][g][c][split][2]: the splits are combined here,
+// weight 2^(m_split - M) / L each.  `pairs` may be null: then `direct` [T, H D] (type T) is the
 // attention's plain result and only the gate is applied; `talk` and `gate` may each be null.
 template <typename T>
 __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
-    const float* __restrict__ pairs, const T* __restrict__ direct, int ldi,
-    const float* __restrict__ talk, const T* __restrict__ gate, int ldg, T* __restrict__ out, int ldo,
-    int H, int Hkv, int D) {
+    const float* __restrict__ pairs, const float* __restrict__ pair_ml, int splits, int nvh,
+    const T* direct, int ldi, const float* __restrict__ talk, const T* __restrict__ gate, int ldg,
+    T* out, int ldo, int H, int Hkv, int D) {
+    extern __shared__ float factor[];              // [H][nvh][splits] when the splits are combined here
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
+    if (pair_ml != nullptr) {
+        for (int i = threadIdx.x; i < H * nvh; i += blockDim.x) {
+            const float* ml = pair_ml + ((size_t)t * H * nvh + i) * splits * 2;
+            float M = -INFINITY;
+            for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, ml[2 * sp]);
+            float L = 0.f;
+            for (int sp = 0; sp < splits; ++sp)
+                if (ml[2 * sp] != -INFINITY) L += ml[2 * sp + 1] * exp2f(ml[2 * sp] - M);
+            for (int sp = 0; sp < splits; ++sp)
+                factor[i * splits + sp] = (L > 0.f && ml[2 * sp] != -INFINITY) ? exp2f(ml[2 * sp] - M) / L : 0.f;
+        }
+        __syncthreads();
+    }
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= H * D) return;
     const int h = idx / D, d = idx - h * D;
     float v;
     if (pairs != nullptr) {
-        const int vh = h / (H / Hkv);
-        const float* p = pairs + (((size_t)t * H) * Hkv + vh) * D + d;
+        const int c = nvh > 1 ? h / (H / Hkv) : 0;
         v = 0.f;
-        for (int g = 0; g < H; ++g)
-            v += (talk != nullptr ? talk[h * H + g] : (g == h ? 1.f : 0.f)) * p[(size_t)g * Hkv * D];
+        const int g_lo = talk != nullptr ? 0 : h, g_hi = talk != nullptr ? H : h + 1;
+        for (int g = g_lo; g < g_hi; ++g) {
+            const float w = talk != nullptr ? talk[h * H + g] : 1.f;
+            const size_t pi = ((size_t)t * H + g) * nvh + c;
+            if (pair_ml != nullptr) {
+                float acc = 0.f;
+                for (int sp = 0; sp < splits; ++sp)
+                    acc += factor[(g * nvh + c) * splits + sp] * pairs[(pi * splits + sp) * D + d];
+                v += w * acc;
+            } else {
+                v += w * pairs[pi * D + d];
+            }
+        }
     } else {
         v = to_float(direct[(size_t)t * ldi + idx]);
     }
@@ -252,14 +281,20 @@ __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
 }
 
 template <typename T>
-static int launch_mix(const float* pairs, const T* direct, int ldi, const float* talk, const T* gate,
-                      int ldg, T* out, int ldo, int T_tokens, int H, int Hkv, int D, cudaStream_t st) {
+static int launch_mix(const float* pairs, const float* pair_ml, int splits, int nvh, const T* direct,
+                      int ldi, const float* talk, const T* gate, int ldg, T* out, int ldo, int T_tokens,
+                      int H, int Hkv, int D, cudaStream_t st) {
     if (T_tokens <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || T_tokens > 65535 ||
         (pairs == nullptr) == (direct == nullptr))
         return SLB_ERR_BAD_ARG;
-    return slb_launch(mix_heads_gate_kernel<T>, dim3((H * D + 255) / 256, T_tokens), dim3(256), 0, st,
-                      pairs, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
+    if (pairs != nullptr && ((nvh != 1 && nvh != Hkv) || (talk != nullptr && nvh != Hkv && Hkv != 1)))
+        return SLB_ERR_BAD_ARG;
+    if (pair_ml != nullptr && (pairs == nullptr || splits < 1)) return SLB_ERR_BAD_ARG;
+    const size_t smem = pair_ml != nullptr ? (size_t)H * nvh * splits * sizeof(float) : 0;
+    if (smem > 48 * 1024) return SLB_ERR_TOO_LARGE;
+    return slb_launch(mix_heads_gate_kernel<T>, dim3((H * D + 255) / 256, T_tokens), dim3(256), smem, st,
+                      pairs, pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
 }
 
 extern "C" {
@@ -283,15 +318,17 @@ int slb_paged_attention_generic_bf16(const bf16* q, int ldq, const bf16* kc, con
                                  tile_seq, tile_row0, num_tiles, H, Hkv, D, ps, num_pages, scale, window,
                                  bias_r1, bias_r2, pair_out, st);
 }
-int slb_mix_heads_gate_f32(const float* pairs, const float* direct, int ldi, const float* talk,
-                           const float* gate, int ldg, float* out, int ldo, int T_tokens, int H, int Hkv,
-                           int D, cudaStream_t st) {
-    return launch_mix<float>(pairs, direct, ldi, talk, gate, ldg, out, ldo, T_tokens, H, Hkv, D, st);
+int slb_mix_heads_gate_f32(const float* pairs, const float* pair_ml, int splits, int nvh,
+                           const float* direct, int ldi, const float* talk, const float* gate, int ldg,
+                           float* out, int ldo, int T_tokens, int H, int Hkv, int D, cudaStream_t st) {
+    return launch_mix<float>(pairs, pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, T_tokens,
+                             H, Hkv, D, st);
 }
-int slb_mix_heads_gate_bf16(const float* pairs, const bf16* direct, int ldi, const float* talk,
-                            const bf16* gate, int ldg, bf16* out, int ldo, int T_tokens, int H, int Hkv,
-                            int D, cudaStream_t st) {
-    return launch_mix<bf16>(pairs, direct, ldi, talk, gate, ldg, out, ldo, T_tokens, H, Hkv, D, st);
+int slb_mix_heads_gate_bf16(const float* pairs, const float* pair_ml, int splits, int nvh,
+                            const bf16* direct, int ldi, const float* talk, const bf16* gate, int ldg,
+                            bf16* out, int ldo, int T_tokens, int H, int Hkv, int D, cudaStream_t st) {
+    return launch_mix<bf16>(pairs, pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, T_tokens,
+                            H, Hkv, D, st);
 }
 // rows per tile of the generic kernel (the host builds the tile list with it)
 int slb_paged_attention_generic_tile_rows() { return AG_BM; }

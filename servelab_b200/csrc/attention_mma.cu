@@ -19,6 +19,14 @@
 // Masking: key r is visible to a query at position a iff r <= a and, with a
 // window w > 0, a - r < w.  Page layout: [page][kv head][slot][SLB_HEAD_DIM].
 //
+// Both kernels also exist in a second instance (TALK) for mixers that change scores and
+// weights: a log-distance bias r1_h ln(1 + r2_h (a - r)) is subtracted from the scaled score,
+// the values may come from another kv head than the keys (the grid names it), and the
+// result leaves in float32 per (query head, value head) pair -- normalised from the prefill
+// kernel, as unnormalised split partials with their (max, sum) from the decode kernel -- for
+// the kernel that mixes heads after the softmax (slb_mix_heads_gate in the core library),
+// which also combines the decode kernel's splits.
+//
 // Reference analogue: the one-program-per-(sequence, head) Triton decode kernel
 // (servelab/attention/triton/paged_attention.py:25-74), which has no tensor-core
 // path, no sharing of loads across a group and no split of long contexts, and the
@@ -59,7 +67,7 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
                                                   const bf16* __restrict__ kc,
                                                   const bf16* __restrict__ vc,
                                                   const int* __restrict__ table, int k0, int kend,
-                                                  int kvh, int Hkv, int ps, int num_pages) {
+                                                  int kvh, int vh, int Hkv, int ps, int num_pages) {
     static_assert(NTHREADS == 2 * BN, "one row of K or V per thread");
     const int r = threadIdx.x & (BN - 1);
     const bool is_v = threadIdx.x >= BN;
@@ -79,7 +87,7 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
     }
     bf16* dst = (is_v ? Vs : Ks) + r * LDS;
     if (ok) {
-        const bf16* src = (is_v ? vc : kc) + (((size_t)page * Hkv + kvh) * ps + slot) * D;
+        const bf16* src = (is_v ? vc : kc) + (((size_t)page * Hkv + (is_v ? vh : kvh)) * ps + slot) * D;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive_expect_tx(bar, D * 2);
         bulk_copy_g2s(dst, src, D * 2, bar);
@@ -95,7 +103,7 @@ __device__ __forceinline__ void load_kv_tile_bulk(bf16* Ks, bf16* Vs, uint64_t* 
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc,
                                              const bf16* __restrict__ vc,
                                              const int* __restrict__ table, int k0, int kend,
-                                             int kvh, int Hkv, int ps, int num_pages) {
+                                             int kvh, int vh, int Hkv, int ps, int num_pages) {
     const bool pow2 = (ps & (ps - 1)) == 0;
     const int shift = __ffs(ps) - 1;
     for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += NTHREADS) {
@@ -111,9 +119,9 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
             page = -1;
         }
         ok = ok && page >= 0;
-        const size_t off = ok ? (((size_t)page * Hkv + kvh) * ps + slot) * D + c * 8 : 0;
-        cp_async16(Ks + r * LDS + c * 8, kc + off, ok);
-        cp_async16(Vs + r * LDS + c * 8, vc + off, ok);
+        const size_t base = ok ? ((size_t)page * Hkv * ps + slot) * D + c * 8 : 0;
+        cp_async16(Ks + r * LDS + c * 8, kc + base + (ok ? (size_t)kvh * ps * D : 0), ok);
+        cp_async16(Vs + r * LDS + c * 8, vc + base + (ok ? (size_t)vh * ps * D : 0), ok);
     }
 }
 
@@ -226,13 +234,75 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NT_O]
     }
 }
 
+// What the TALK instances add to a launch.
+struct TalkArgs {
+    const float* r1;       // [H] distance bias: r1_h ln(1 + r2_h distance) leaves the scaled score
+    const float* r2;       // [H]
+    float* pair_o;         // prefill: [T][H][nvh][D] normalised; decode: [S][H][nvh][splits][D] partial
+    float* pair_ml;        // decode: [S][H][nvh][splits][2] (max in the base-2 domain, sum)
+    int nvh;               // value heads per query head: Hkv (every pair) or 1 (its own kv head only)
+};
+
+// softmax_tile for scores with the distance bias (always masked: the bias needs every
+// distance anyway).  (r1, r2) per row half; r1 is applied in the base-2 domain, where
+// r1 ln(x) log2(e) = r1 log2(x).
+template <int NT>
+__device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&o)[NT_O][4], float (&m)[2],
+                                                  float (&l)[2], int kpos0, int kend, int pos_lo,
+                                                  int pos_hi, int window, float scale_log2,
+                                                  const float (&r1)[2], const float (&r2)[2]) {
+    const int tig = threadIdx.x & 3;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kp = kpos0 + j * 8 + tig * 2 + (e & 1);
+            const int pos = (e < 2) ? pos_lo : pos_hi;
+            const bool vis = kp < kend && kp <= pos && (window <= 0 || pos - kp < window);
+            s[j][e] = vis ? fmaf(s[j][e], scale_log2, -r1[e >> 1] * log2f(fmaf(r2[e >> 1], (float)(pos - kp), 1.f)))
+                          : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+        }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[h] = exp2f(m[h] - m_use);
+        m[h] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            s[j][2 * h] = exp2f(s[j][2 * h] - m_use);
+            s[j][2 * h + 1] = exp2f(s[j][2 * h + 1] - m_use);
+            sum += s[j][2 * h] + s[j][2 * h + 1];
+        }
+        l[h] = l[h] * alpha[h] + sum;
+    }
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) {
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1];
+            o[n][3] *= alpha[1];
+        }
+    }
+}
+
 // ------------------------------------------------------------------- prefill
+// TALK: grid (tiles x Hkv, nvh); blockIdx.y names the value head when nvh > 1.
+template <bool TALK>
 __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, int H, int Hkv, int ps,
-    int num_pages, float scale_log2, int window) {
+    int num_pages, float scale_log2, int window, TalkArgs ta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS], later the output stage
@@ -243,6 +313,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     // started first, all kv heads of a tile together (blocks start in the order of their
     // linear index)
     const int kvh = blockIdx.x % Hkv;
+    const int vh = (TALK && ta.nvh > 1) ? (int)blockIdx.y : kvh;
     const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
@@ -272,13 +343,18 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const int kend = p_last + 1;
     const int ntiles = (kend - kbeg + BN - 1) / BN;
 
-    load_kv_tile(stage0, stage0 + BN * LDS, kc, vc, table, kbeg, kend, kvh, Hkv, ps, num_pages);
+    load_kv_tile(stage0, stage0 + BN * LDS, kc, vc, table, kbeg, kend, kvh, vh, Hkv, ps, num_pages);
     cp_async_commit();
 
     // this thread's two rows
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
+    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
+    if (TALK && ta.r1 != nullptr) {
+        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + (row0 + r_lo) % g]; br2[0] = ta.r2[kvh * g + (row0 + r_lo) % g]; }
+        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + (row0 + r_hi) % g]; br2[1] = ta.r2[kvh * g + (row0 + r_hi) % g]; }
+    }
     const int wr_last = min(nrows - 1, warp * 16 + 15);
     const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
     const bool warp_rows_full = warp * 16 + 15 < nrows;
@@ -297,7 +373,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
         bf16* Vs = Ks + BN * LDS;
         if (t + 1 < ntiles) {
             bf16* Kn = stage0 + ((t + 1) & 1) * STAGE_ELEMS;
-            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kbeg + (t + 1) * BN, kend, kvh, Hkv, ps, num_pages);
+            load_kv_tile(Kn, Kn + BN * LDS, kc, vc, table, kbeg + (t + 1) * BN, kend, kvh, vh, Hkv, ps, num_pages);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -312,7 +388,9 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
             // all 64 keys visible to all 16 rows of the warp: no mask to evaluate
             const bool open = warp_rows_full && k0 + BN - 1 <= warp_pos_min &&
                               (window <= 0 || warp_pos_max - k0 < window);
-            if (open)
+            if (TALK)
+                softmax_tile_bias<BN / 8>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            else if (open)
                 softmax_tile<BN / 8, false>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<BN / 8, true>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
@@ -330,6 +408,24 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     }
     const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f;
     const float inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    if (TALK) {
+        // float32 results of this (query head, value head) pair, straight from the registers
+        const int vhi = ta.nvh > 1 ? vh : 0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = half ? r_hi : r_lo;
+            if (row >= nrows) continue;
+            const int rho = row0 + row;
+            const int tl = rho / g, hg = rho - tl * g;
+            const float inv = half ? inv_hi : inv_lo;
+            float* dst = ta.pair_o + (((size_t)(q0 + tl) * H + (size_t)(kvh * g + hg)) * ta.nvh + vhi) * D +
+                         (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+        }
+        return;
+    }
     bf16* Os = Qs + warp * 16 * LDS;
     __syncwarp();
 #pragma unroll
@@ -355,11 +451,15 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
 // grid (num_splits, Hkv * head_tiles, S); q_len must be 1 for every request.
 // Scratch: part_o [S][H][num_splits][D] float32 (unnormalised), part_ml
 // [S][H][num_splits][2] float32 (running max in the base-2 domain, running sum).
+// TALK: grid (num_splits * nvh, Hkv * head_tiles, S); results always leave as partials in
+// ta.pair_o / ta.pair_ml (the kernel that mixes the heads combines the splits).
+template <bool TALK>
 __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ ctx_len, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles) {
+    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles,
+    TalkArgs ta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
@@ -369,8 +469,10 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     __shared__ __align__(8) uint64_t full_bar[DSTAGES];    // a stage's K and V rows have landed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x;
+    const int split = TALK ? blockIdx.x % num_splits : blockIdx.x;
     const int kvh = blockIdx.y / head_tiles, htile = blockIdx.y - kvh * head_tiles;
+    const int vh = (TALK && ta.nvh > 1) ? (int)(blockIdx.x / num_splits) : kvh;
+    const int vhi = (TALK && ta.nvh > 1) ? vh : 0;
     const int s = blockIdx.z;
     const int g = H / Hkv;
     const int h0 = htile * 16;                             // first head of the group in this tile
@@ -407,7 +509,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         if (p < ntiles) {
             bf16* Kp = stage0 + p * STAGE_ELEMS;
             load_kv_tile_bulk(Kp, Kp + BN * LDS, &full_bar[p], kc, vc, table, kstart + p * BN, ctx,
-                              kvh, Hkv, ps, num_pages);
+                              kvh, vh, Hkv, ps, num_pages);
         }
     }
     cp_async_wait<0>();                                     // the Q tile
@@ -415,6 +517,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos : -1;
     const int pos_hi = r_hi < nrows ? pos : -1;
+    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
+    if (TALK && ta.r1 != nullptr) {
+        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + h0 + r_lo]; br2[0] = ta.r2[kvh * g + h0 + r_lo]; }
+        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + h0 + r_hi]; br2[1] = ta.r2[kvh * g + h0 + r_hi]; }
+    }
     unsigned qf[KSTEPS][4];
     float o[NT_O][4];
 #pragma unroll
@@ -431,7 +538,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
         if (tn < ntiles) {
             bf16* Kn = stage0 + (tn % DSTAGES) * STAGE_ELEMS;
             load_kv_tile_bulk(Kn, Kn + BN * LDS, &full_bar[tn % DSTAGES], kc, vc, table,
-                              kstart + tn * BN, ctx, kvh, Hkv, ps, num_pages);
+                              kstart + tn * BN, ctx, kvh, vh, Hkv, ps, num_pages);
         }
         ok = mbar_wait(&full_bar[t % DSTAGES], (t / DSTAGES) & 1);
         if (t == 0) {
@@ -443,7 +550,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
             // every key of this warp's 16 is inside the context and the window: no mask
-            if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
+            if (TALK)
+                softmax_tile_bias<2>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            else if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
                 softmax_tile<2, false>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
@@ -458,7 +567,13 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
                 mbar_wait(&full_bar[tt % DSTAGES], (tt / DSTAGES) & 1);
             // the combine step must not merge what an earlier launch left in these slots:
             // mark this split of every head as empty (maximum -inf, sum 0)
-            if (num_splits > 1 && tid < nrows) {
+            if (TALK) {
+                if (tid < nrows) {
+                    const size_t pi = (((size_t)s * H + kvh * g + h0 + tid) * ta.nvh + vhi) * num_splits + split;
+                    ta.pair_ml[pi * 2] = -INFINITY;
+                    ta.pair_ml[pi * 2 + 1] = 0.f;
+                }
+            } else if (num_splits > 1 && tid < nrows) {
                 const size_t pi = ((size_t)s * H + kvh * g + h0 + tid) * num_splits + split;
                 part_ml[pi * 2] = -INFINITY;
                 part_ml[pi * 2 + 1] = 0.f;
@@ -503,7 +618,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             }
         }
         const int head = kvh * g + h0 + r;
-        if (num_splits == 1) {
+        if (TALK) {
+            const size_t pi = (((size_t)s * H + head) * ta.nvh + vhi) * num_splits + split;
+            ta.pair_o[pi * D + d] = acc;
+            if (d == 0) { ta.pair_ml[pi * 2] = M; ta.pair_ml[pi * 2 + 1] = L; }
+        } else if (num_splits == 1) {
             out[(size_t)s * ldo + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
             const size_t pi = ((size_t)s * H + head) * num_splits + split;
@@ -583,11 +702,60 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
         return SLB_ERR_BAD_ARG;                            // 16-byte copies
     if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;              // a bit per device
-    const int crc = slb_configure(&configured, prefill_attention_kernel, PREFILL_SMEM);
+    const int crc = slb_configure(&configured, prefill_attention_kernel<false>, PREFILL_SMEM);
     if (crc != 0) return crc;
-    return slb_launch(prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
+    return slb_launch(prefill_attention_kernel<false>, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
                       q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window);
+                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window, TalkArgs{});
+}
+
+// The TALK instance of the prefill kernel: pair_o float32 [T][H][nvh][D], nvh = Hkv when
+// every_pair (each query head's weights applied to every kv head's values), else 1.
+int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
+                                    const int* block_table, int max_pages, const int* cu_q,
+                                    const int* ctx_len, const int* tile_seq, const int* tile_row0,
+                                    int num_tiles, int H, int Hkv, int ps, int num_pages, float scale,
+                                    int window, const float* r1, const float* r2, float* pair_o,
+                                    int every_pair, cudaStream_t st) {
+    if (num_tiles <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) ||
+        pair_o == nullptr || (r1 == nullptr) != (r2 == nullptr))
+        return SLB_ERR_BAD_ARG;
+    if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16 || (uintptr_t)pair_o % 8) return SLB_ERR_BAD_ARG;
+    if ((long long)num_tiles * Hkv > 0x7fffffffll || Hkv > 65535) return SLB_ERR_TOO_LARGE;
+    static unsigned long long configured = 0;
+    const int crc = slb_configure(&configured, prefill_attention_kernel<true>, PREFILL_SMEM);
+    if (crc != 0) return crc;
+    const int nvh = every_pair ? Hkv : 1;
+    return slb_launch(prefill_attention_kernel<true>, dim3((unsigned)num_tiles * Hkv, nvh), dim3(NTHREADS),
+                      PREFILL_SMEM, st, q, ldq, kc, vc, (bf16*)nullptr, 0, block_table, max_pages, cu_q, ctx_len,
+                      tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
+                      TalkArgs{r1, r2, pair_o, nullptr, nvh});
+}
+
+// The TALK instance of the decode kernel: partials pair_o float32 [S][H][nvh][splits][D] and
+// pair_ml [S][H][nvh][splits][2]; nothing is combined here.
+int slb_talk_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
+                                   const int* block_table, int max_pages, const int* ctx_len, int S,
+                                   int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                   int num_splits, const float* r1, const float* r2, float* pair_o,
+                                   float* pair_ml, int every_pair, cudaStream_t st) {
+    if (S <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) ||
+        pair_o == nullptr || pair_ml == nullptr || (r1 == nullptr) != (r2 == nullptr) || num_splits < 1)
+        return SLB_ERR_BAD_ARG;
+    if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;
+    const int nvh = every_pair ? Hkv : 1;
+    const int g = H / Hkv;
+    const int head_tiles = (g + 15) / 16;
+    if (num_splits > MAX_SPLITS || S > 65535 || Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
+    static unsigned long long configured = 0;
+    const int crc = slb_configure(&configured, decode_attention_kernel<true>, DECODE_SMEM);
+    if (crc != 0) return crc;
+    return slb_launch(decode_attention_kernel<true>, dim3(num_splits * nvh, Hkv * head_tiles, S), dim3(NTHREADS),
+                      DECODE_SMEM, st, q, ldq, kc, vc, (bf16*)nullptr, 0, block_table, max_pages, ctx_len,
+                      (float*)nullptr, (float*)nullptr, H, Hkv, ps, num_pages, scale * 1.4426950408889634f,
+                      window, num_splits, head_tiles, TalkArgs{r1, r2, pair_o, pair_ml, nvh});
 }
 
 // scratch: float32 buffer of at least slb_decode_attention_scratch_bytes(...) bytes
@@ -606,14 +774,14 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
     const int head_tiles = (g + 15) / 16;
     if (Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;              // a bit per device
-    const int crc = slb_configure(&configured, decode_attention_kernel, DECODE_SMEM);
+    const int crc = slb_configure(&configured, decode_attention_kernel<false>, DECODE_SMEM);
     if (crc != 0) return crc;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
-    const int rc = slb_launch(decode_attention_kernel, dim3(num_splits, Hkv * head_tiles, S),
+    const int rc = slb_launch(decode_attention_kernel<false>, dim3(num_splits, Hkv * head_tiles, S),
                               dim3(NTHREADS), DECODE_SMEM, st, q, ldq, kc, vc, out, ldo, block_table,
                               max_pages, ctx_len, part_o, part_ml, H, Hkv, ps, num_pages,
-                              scale * 1.4426950408889634f, window, num_splits, head_tiles);
+                              scale * 1.4426950408889634f, window, num_splits, head_tiles, TalkArgs{});
     if (rc != 0 || num_splits == 1) return rc;
     return slb_launch(decode_combine_kernel, dim3(H, S), dim3((D + 31) / 32 * 32), 0, st,
                       (const float*)part_o, (const float*)part_ml, out, ldo, H, num_splits);

@@ -50,8 +50,17 @@ def paged_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, 
 
 
 # ---------------------------------------------- attention with mixed heads
+use_talk_fast = True       # bfloat16: the tensor-core instances (off: the plain kernel, their twin)
+
+
+def _talk_fast(head_dim: int, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and use_talk_fast and not force_generic and K.has_fast_attention(head_dim)
+
+
 def prepare_talk_attention(head_dim: int, dtype: torch.dtype) -> None:
     """Builds what ``talk_attention`` will launch for this head size (at load, not in a step)."""
+    if _talk_fast(head_dim, dtype) and torch.cuda.is_available():
+        L.attention(head_dim)
 
 
 def talk_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, scale, window,
@@ -59,10 +68,23 @@ def talk_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, s
     """Windowed attention with a log-distance bias, then the heads' softmax weights mixed by
     ``talk`` [H, H] (None: not mixed) and the result multiplied by sigmoid(``gate``) (None:
     not gated), into ``out`` [T, H D].  Mixed heads go through the results of every (query
-    head, kv head) pair, float32 [T, H, Hkv, D], which ``mix_heads_gate`` combines."""
+    head, kv head) pair, float32 [T, H, Hkv, D], which ``mix_heads_gate`` combines (with the
+    key splits of a decode step).  float32: the plain kernel; bfloat16: the tensor-core
+    instances (decode kernel for steps of single tokens, prefill kernel otherwise)."""
     T = q.shape[0]
-    g = H // Hkv
-    tile_seq, tile_row0, n = ctx.attention_tiles(g, K.generic_attention_tile_rows())
+    nvh = Hkv if talk is not None else 1
+    if _talk_fast(D, q.dtype):
+        if ctx.decode_only and use_decode_kernel:
+            pairs, pair_ml = K.talk_decode_attention(ctx, q, k_cache, v_cache, table, H, Hkv, D,
+                                                     page_size, scale, window, bias_r1, bias_r2, nvh)
+            K.mix_heads_gate(pairs, None, talk, gate, out, H, Hkv, D, pair_ml)
+            return
+        pairs = torch.empty((T, H, nvh, D), dtype=torch.float32, device=q.device)
+        K.talk_prefill_attention(ctx, q, k_cache, v_cache, table, H, Hkv, D, page_size, scale, window,
+                                 bias_r1, bias_r2, pairs)
+        K.mix_heads_gate(pairs, None, talk, gate, out, H, Hkv, D)
+        return
+    tile_seq, tile_row0, n = ctx.attention_tiles(H // Hkv, K.generic_attention_tile_rows())
     if talk is None:
         K.paged_attention_generic(q, k_cache, v_cache, out, table, ctx.cu_q, ctx.ctx_len, tile_seq,
                                   tile_row0, n, H, Hkv, D, page_size, scale, window, bias_r1, bias_r2)

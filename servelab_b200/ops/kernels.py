@@ -249,14 +249,66 @@ def paged_attention_generic(q, k_cache, v_cache, out, block_table, cu_q, ctx_len
 
 def mix_heads_gate(pairs: Optional[torch.Tensor], direct: Optional[torch.Tensor],
                    talk: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
-                   num_heads: int, num_kv_heads: int, head_dim: int) -> None:
-    """out[t, h] = (sum_g talk[h, g] pairs[t, g, kv(h)]) * sigmoid(gate[t, h]); with ``pairs``
-    None, ``direct`` [T, H D] takes the place of the sum.  ``gate`` [T, H D] may be a view of
-    a wider projection (its row stride is passed); ``talk`` float32 [H, H]."""
+                   num_heads: int, num_kv_heads: int, head_dim: int,
+                   pair_ml: Optional[torch.Tensor] = None) -> None:
+    """out[t, h] = (sum_g talk[h, g] pairs[t, g, c(h)]) * sigmoid(gate[t, h]); with ``pairs``
+    None, ``direct`` [T, H D] takes the place of the sum.  ``pairs`` float32 [T, H, nvh, D]
+    (nvh = Hkv, or 1 without ``talk``), or with ``pair_ml`` [T, H, nvh, splits, 2] the
+    unnormalised partials [T, H, nvh, splits, D] of split key ranges, combined here.  ``gate``
+    [T, H D] may be a view of a wider projection (its row stride is passed); ``talk`` float32
+    [H, H]."""
     fn = getattr(L.core(), "slb_mix_heads_gate_" + _suffix(out.dtype))
-    L.check(fn(_p(pairs), _p(direct), direct.stride(0) if direct is not None else 0, _p(talk),
+    splits = pair_ml.shape[3] if pair_ml is not None else 0
+    nvh = pairs.shape[2] if pairs is not None else 0
+    L.check(fn(_p(pairs), _p(pair_ml), splits, nvh, _p(direct),
+               direct.stride(0) if direct is not None else 0, _p(talk),
                _p(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0),
                out.shape[0], num_heads, num_kv_heads, head_dim, _stream()), "mix_heads_gate")
+
+
+def talk_prefill_attention(ctx, q, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim,
+                           page_size, scale, window, bias_r1, bias_r2, pairs: torch.Tensor) -> None:
+    """The tensor-core prefill attention with a distance bias, results per (query head, value
+    head) pair in ``pairs`` float32 [T, H, nvh, D] (nvh = Hkv: every pair; 1: own kv head)."""
+    lib = L.attention(head_dim)
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads,
+                                                 lib.slb_prefill_attention_tile_rows())
+    L.check(lib.slb_talk_prefill_attention_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(), tile_seq.data_ptr(),
+        tile_row0.data_ptr(), n, num_heads, num_kv_heads, page_size, k_cache.shape[0], float(scale),
+        int(window), _p(bias_r1), _p(bias_r2), pairs.data_ptr(), 1 if pairs.shape[2] > 1 or num_kv_heads == 1 else 0,
+        _stream()), "talk_prefill_attention")
+
+
+def talk_decode_splits(num_seqs: int, num_kv_heads: int, group: int, nvh: int, longest_context: int,
+                       window: int, max_splits: int) -> int:
+    """Key splits of the decode kernel for mixed heads: enough blocks for ``decode_ctas_per_sm``
+    per SM, at most one split per 64 keys a query can see."""
+    seen = min(longest_context, window + 63) if window > 0 else longest_context
+    ctas = num_seqs * num_kv_heads * nvh * ((group + 15) // 16)
+    want = max(1, (decode_ctas_per_sm * _num_sms()) // max(ctas, 1))
+    return max(1, min(want, max_splits, -(-seen // 64)))
+
+
+def talk_decode_attention(ctx, q, k_cache, v_cache, block_table, num_heads, num_kv_heads, head_dim,
+                          page_size, scale, window, bias_r1, bias_r2, nvh: int):
+    """The split-key decode attention with a distance bias for steps of single tokens; returns
+    (pairs [S, H, nvh, splits, D], pair_ml [S, H, nvh, splits, 2]), float32 partials that
+    ``mix_heads_gate`` combines."""
+    lib = L.attention(head_dim)
+    S = ctx.num_seqs
+    splits = talk_decode_splits(S, num_kv_heads, num_heads // num_kv_heads, nvh, ctx.split_hint_len,
+                                window, lib.slb_decode_attention_max_splits())
+    pairs = torch.empty((S, num_heads, nvh, splits, head_dim), dtype=_F32, device=q.device)
+    pair_ml = torch.empty((S, num_heads, nvh, splits, 2), dtype=_F32, device=q.device)
+    L.check(lib.slb_talk_decode_attention_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], ctx.ctx_len.data_ptr(), S, num_heads, num_kv_heads, page_size,
+        k_cache.shape[0], float(scale), int(window), splits, _p(bias_r1), _p(bias_r2),
+        pairs.data_ptr(), pair_ml.data_ptr(), 1 if nvh > 1 or num_kv_heads == 1 else 0, _stream()),
+        "talk_decode_attention")
+    return pairs, pair_ml
 
 
 def dyt_add_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], post, pre,

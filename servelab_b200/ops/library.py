@@ -37,8 +37,8 @@ _CORE_SIGNATURES = {
     "slb_cache_write_status": [I],
     "slb_paged_attention_generic_f32": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P],
     "slb_paged_attention_generic_bf16": [P, I, P, P, P, I, P, I, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, P],
-    "slb_mix_heads_gate_f32": [P, P, I, P, P, I, P, I, I, I, I, I, P],
-    "slb_mix_heads_gate_bf16": [P, P, I, P, P, I, P, I, I, I, I, I, P],
+    "slb_mix_heads_gate_f32": [P, P, I, I, P, I, P, P, I, P, I, I, I, I, I, P],
+    "slb_mix_heads_gate_bf16": [P, P, I, I, P, I, P, P, I, P, I, I, I, I, I, P],
     "slb_dyt_add_norm_f32": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
     "slb_dyt_add_norm_bf16": [P, I, P, I, P, P, P, P, P, P, P, I, P, I, I, P],
     "slb_qk_conv_cache_f32": [P, I, P, I, P, P, P, P, P, P, I, I, I, F, I, P, I, P, I, I, I, I, I, I, P],
@@ -170,6 +170,8 @@ _ATTN_SIGNATURES = {
     "slb_decode_attention_ws_splits_used": [I],
     "slb_decode_attention_ws_max_splits": [],
     "slb_decode_attention_ws_tile_keys": [],
+    "slb_talk_prefill_attention_bf16": [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P, P, P, I, P],
+    "slb_talk_decode_attention_bf16": [P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, P, P, P, I, P],
 }
 
 

@@ -32,7 +32,7 @@ from ..cache.manager import FixedStateRequest, PagedKVRequest
 from ..ops import attention as A
 from ..ops import kernels as K
 from ..ops.linear import linear
-from ..weights.source import BIAS, MATRIX, TensorDecl
+from ..weights.source import BIAS, MATRIX, MIXING, POSITIVE, TensorDecl
 from .base import Mixer
 from .registry import register_mixer
 
@@ -70,10 +70,10 @@ class ConvTalkAttention(Mixer):
             out += [TensorDecl(n["q"] + spec.conv_suffix, (q, spec.conv_taps), BIAS),
                     TensorDecl(n["k"] + spec.conv_suffix, (kv, spec.conv_taps), BIAS)]
         if spec.distance_bias:
-            out += [TensorDecl(f"{prefix}.{spec.bias_r1_name}", (spec.num_heads,), BIAS),
-                    TensorDecl(f"{prefix}.{spec.bias_r2_name}", (spec.num_heads,), BIAS)]
+            out += [TensorDecl(f"{prefix}.{spec.bias_r1_name}", (spec.num_heads,), POSITIVE),
+                    TensorDecl(f"{prefix}.{spec.bias_r2_name}", (spec.num_heads,), POSITIVE)]
         if spec.talking_heads:
-            out.append(TensorDecl(f"{prefix}.{spec.talk_name}", (spec.num_heads, spec.num_heads), BIAS))
+            out.append(TensorDecl(f"{prefix}.{spec.talk_name}", (spec.num_heads, spec.num_heads), MIXING))
         if spec.output_gate:
             out.append(TensorDecl(n["gate"], (q, h), MATRIX))
         return out

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels as K
-from ..weights.source import BIAS, NORM, TensorDecl
+from ..weights.source import BIAS, NORM, POSITIVE, TensorDecl
 from .base import Norm
 from .registry import register_norm
 
@@ -72,7 +72,7 @@ class DynamicTanh(Norm):
     def declare(cls, spec, prefix):
         return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), NORM),
                 TensorDecl(prefix + spec.bias_suffix, (spec.dim,), BIAS),
-                TensorDecl(prefix + spec.alpha_suffix, (), BIAS)]
+                TensorDecl(prefix + spec.alpha_suffix, (), POSITIVE)]
 
     def load(self, store):
         s = self.spec

@@ -115,5 +115,5 @@ def write_safetensors(path: str, decls: Iterable[Tuple[str, Tuple[int, ...], tor
             if tuple(t.shape) != tuple(shape) or t.dtype != dt:
                 raise ValueError(f"tensor {name}: produced {tuple(t.shape)} {t.dtype}, "
                                  f"declared {tuple(shape)} {dt}")
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
     os.replace(tmp, path)

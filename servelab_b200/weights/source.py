@@ -30,6 +30,8 @@ MATRIX = "matrix"     # GEMM operand or embedding table: N(0, std)
 BIAS = "bias"         # additive vector: N(0, std); kept in float32
 NORM = "norm"         # multiplicative norm weight: 1 + N(0, norm_std); kept in float32
 TABLE = "table"       # integer table: kept as int32
+POSITIVE = "positive"  # positive numbers (a norm's scalar gain, decay rates): 0.05 + |N(0, 0.5^2)|; float32
+MIXING = "mixing"     # a square matrix that mixes channels or heads: identity + N(0, 0.2^2); float32
 
 
 @dataclass(frozen=True)
@@ -146,7 +148,8 @@ class RandomSource(WeightSource):
 
     Each tensor has its own generator seeded by (seed, crc32(name)), so a tensor
     does not depend on which others are drawn or in what order.  Matrices and
-    biases are N(0, std^2); norm weights 1 + N(0, norm_std^2).  On a CUDA
+    biases are N(0, std^2); norm weights 1 + N(0, norm_std^2); positive numbers
+    0.05 + |N(0, 0.5^2)|; mixing matrices identity + N(0, 0.2^2).  On a CUDA
     device the draw uses the device generator (fast for billions of values; the
     values then differ from the CPU's for the same seed).
     """
@@ -181,6 +184,10 @@ class RandomSource(WeightSource):
         t = torch.randn(d.shape, generator=gen, device=self.device, dtype=torch.float32)
         if d.role == NORM:
             t.mul_(self.norm_std).add_(1.0)
+        elif d.role == POSITIVE:
+            t.mul_(0.5).abs_().add_(0.05)
+        elif d.role == MIXING:
+            t.mul_(0.2).add_(torch.eye(d.shape[0], d.shape[1], device=t.device))
         else:
             t.mul_(next((v for k, v in self.std_of.items() if k in name), self.std))
         return t.to(self.dtype)

@@ -4,7 +4,7 @@ Policy, by role of the tensor:
   * matrices (GEMM operands, the embedding table) go to the compute dtype:
     bfloat16 for serving, float32 for the 32-bit path (float16 checkpoints are
     converted; no tensor is kept in float16);
-  * norm weights and biases are kept in float32 whatever their stored dtype
+  * norm weights, biases, positive scalars and mixing matrices are kept in float32 whatever their stored dtype
     (exact for bfloat16 sources; a tensor stored in 32-bit stays so), because
     the kernels that use them compute in float32;
   * integer tables become int32.
@@ -16,7 +16,8 @@ from typing import Dict, Iterable, List
 
 import torch
 
-from .source import BIAS, MATRIX, NORM, TABLE, TensorDecl, WeightSource, check_source
+from .source import (BIAS, MATRIX, MIXING, NORM, POSITIVE, TABLE, TensorDecl, WeightSource,
+                     check_source)
 
 
 class WeightStore:
@@ -33,7 +34,7 @@ class WeightStore:
         role = self.decls[name].role
         if role == TABLE:
             return torch.int32
-        if role in (NORM, BIAS):
+        if role in (NORM, BIAS, POSITIVE, MIXING):
             return torch.float32
         return self.compute_dtype
 
