@@ -110,29 +110,56 @@ def _measure(cfg: dict, note) -> Dict[str, object]:
     return out
 
 
-def _attention_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[str, object]:
-    """Achieved fractions of the measured peaks for the attention kernels of both models, per
-    layer.  Decode: bytes of the visible keys (and values, where they are stored) of 8 requests
-    over the kernel's time, of the copy bandwidth.  Prefill: 4 T W' H D flops (scores and
-    weighted values of the visible pairs; W' the mean number of visible keys) over the kernel's
-    time, of the bf16 peak -- the same count for both, so that the fraction says how far each
-    is from the arithmetic the design needs, not from what the kernel happens to do."""
+def _kernel_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[str, object]:
+    """Achieved fractions of the measured peaks for the kernels that differ between the two
+    models, per launch.  Attention, decode: bytes of the visible keys (and values, where they
+    are stored) of 8 requests over the kernel's time, of the copy bandwidth.  Attention,
+    prefill: 4 T W' H D flops (scores and weighted values of the visible pairs; W' the mean
+    number of visible keys) over the kernel's time, of the bf16 peak -- the same count for both
+    models, so that the fraction says how far each is from the arithmetic the design needs, not
+    from what the kernel happens to do.  Elementwise kernels of the 2,048-token prefill: the
+    bytes they must move (float32 stream in and out, update in, normed rows out; projection in,
+    queries and cache rows out; pair results and gate in, rows out) of the copy bandwidth."""
     width, heads, kv, dim, ff = SIZES[size]
     seen = min(CONTEXT, WINDOW)
     pairs = sum(min(t + 1, WINDOW) for t in range(PROMPT))
     flops = 4.0 * pairs * heads * dim
+    qs, ks = heads * dim, kv * dim
     out = {}
+
+    def hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
     for arch, stored, names in (("dezelorn", 1, ("talk_decode_attention", "talk_prefill_attention")),
                                 ("qwen2", 2, ("decode_attention", "prefill_attention_tc"))):
-        dec = res[arch]["decode_b8_kernels_us"].get(names[0])
-        pre = res[arch]["prefill_kernels_us"].get(names[1]) or res[arch]["prefill_kernels_us"].get("prefill_attention")
-        nbytes = 8 * seen * kv * dim * 2 * stored
+        pk, dk = res[arch]["prefill_kernels_us"], res[arch]["decode_b8_kernels_us"]
+        dec = dk.get(names[0])
+        pre = pk.get(names[1]) or pk.get("prefill_attention")
         if dec:
             out[f"{arch}_decode_attention_us"] = round(dec / LAYERS, 2)
-            out[f"{arch}_decode_attention_hbm_frac"] = round(nbytes / (dec / LAYERS * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+            out[f"{arch}_decode_attention_hbm_frac"] = hbm(8 * seen * kv * dim * 2 * stored, dec / LAYERS)
         if pre:
             out[f"{arch}_prefill_attention_us"] = round(pre / LAYERS, 1)
-            out[f"{arch}_prefill_attention_bf16_frac"] = round(flops / (pre / LAYERS * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+            out[f"{arch}_prefill_attention_bf16_frac"] = round(
+                flops / (pre / LAYERS * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+    pk = res["dezelorn"]["prefill_kernels_us"]
+    if pk.get("dyt_add_norm"):
+        us = pk["dyt_add_norm"] / (2 * LAYERS + 1)          # (the last one norms one row only)
+        out["dezelorn_norm_us"], out["dezelorn_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if pk.get("qk_conv_cache"):
+        us = pk["qk_conv_cache"] / LAYERS
+        out["dezelorn_conv_cache_us"], out["dezelorn_conv_cache_hbm_frac"] = round(us, 2), hbm(PROMPT * 4 * (qs + ks), us)
+    if pk.get("mix_heads_gate"):
+        us = pk["mix_heads_gate"] / LAYERS
+        out["dezelorn_mix_gate_us"] = round(us, 2)
+        out["dezelorn_mix_gate_hbm_frac"] = hbm(PROMPT * (4 * heads * kv * dim + 4 * qs), us)
+    pk = res["qwen2"]["prefill_kernels_us"]
+    if pk.get("add_rmsnorm"):
+        us = pk["add_rmsnorm"] / (2 * LAYERS + 1)
+        out["qwen2_norm_us"], out["qwen2_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if pk.get("qkv_rope_cache"):
+        us = pk["qkv_rope_cache"] / LAYERS
+        out["qwen2_rope_cache_us"], out["qwen2_rope_cache_hbm_frac"] = round(us, 2), hbm(PROMPT * 4 * (qs + 2 * ks), us)
     return out
 
 
@@ -147,7 +174,7 @@ def run(peaks, note=lambda m: None, sizes=None) -> Dict[str, object]:
         for arch, make in (("dezelorn", dezelorn_config), ("qwen2", qwen2_config)):
             note(f"{size}: {arch}")
             res[arch] = _measure(make(*dims), note)
-        res["attention"] = _attention_rooflines(size, res, peaks)
+        res["kernels"] = _kernel_rooflines(size, res, peaks)
         res["dims"] = dict(zip(("width", "heads", "kv_heads", "head_dim", "ff"), dims))
         result["sizes"][size] = res
     return result

@@ -231,12 +231,21 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
 // maxima (base-2 domain) and sums in pair_ml[t][g][c][split][2]: the splits are combined here,
 // weight 2^(m_split - M) / L each.  `pairs` may be null: then `direct` [T, H D] (type T) is the
 // attention's plain result and only the gate is applied; `talk` and `gate` may each be null.
-template <typename T>
+// A thread owns one value head c and VEC neighbouring columns d, reads pairs[t][g][c][d] once for
+// every query head g and finishes, MIX_HEADS at a time, the heads of group c from it (the
+// [H, H] matrix sits in shared memory).
+#define MIX_HEADS 8
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
     const float* __restrict__ pairs, const float* __restrict__ pair_ml, int splits, int nvh,
     const T* direct, int ldi, const float* __restrict__ talk, const T* __restrict__ gate, int ldg,
     T* out, int ldo, int H, int Hkv, int D) {
-    extern __shared__ float factor[];              // [H][nvh][splits] when the splits are combined here
+    extern __shared__ float mix_smem[];
+    float* talk_s = mix_smem;                      // [H][H] (with talk)
+    float* factor = mix_smem + (talk != nullptr ? H * H : 0);   // [H][nvh][splits] (with pair_ml)
+    if (talk != nullptr)
+        for (int i = threadIdx.x; i < H * H; i += blockDim.x) talk_s[i] = talk[i];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y;
@@ -251,33 +260,76 @@ __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
             for (int sp = 0; sp < splits; ++sp)
                 factor[i * splits + sp] = (L > 0.f && ml[2 * sp] != -INFINITY) ? exp2f(ml[2 * sp] - M) / L : 0.f;
         }
-        __syncthreads();
     }
+    __syncthreads();
+    const int g = H / Hkv;
+    const int dv = D / VEC;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= H * D) return;
-    const int h = idx / D, d = idx - h * D;
-    float v;
-    if (pairs != nullptr) {
-        const int c = nvh > 1 ? h / (H / Hkv) : 0;
-        v = 0.f;
-        const int g_lo = talk != nullptr ? 0 : h, g_hi = talk != nullptr ? H : h + 1;
-        for (int g = g_lo; g < g_hi; ++g) {
-            const float w = talk != nullptr ? talk[h * H + g] : 1.f;
-            const size_t pi = ((size_t)t * H + g) * nvh + c;
-            if (pair_ml != nullptr) {
-                float acc = 0.f;
-                for (int sp = 0; sp < splits; ++sp)
-                    acc += factor[(g * nvh + c) * splits + sp] * pairs[(pi * splits + sp) * D + d];
-                v += w * acc;
-            } else {
-                v += w * pairs[pi * D + d];
+    if (idx >= Hkv * dv) return;
+    const int c = idx / dv, d = (idx - c * dv) * VEC;       // the kv head whose group is finished, columns
+    for (int h0 = c * g; h0 < (c + 1) * g; h0 += MIX_HEADS) {
+        const int nh = min(MIX_HEADS, (c + 1) * g - h0);
+        float acc[MIX_HEADS][VEC];
+#pragma unroll
+        for (int i = 0; i < MIX_HEADS; ++i)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[i][v] = 0.f;
+        if (pairs == nullptr) {
+#pragma unroll
+            for (int i = 0; i < MIX_HEADS; ++i)
+#pragma unroll
+                for (int v = 0; v < VEC; ++v)
+                    if (i < nh) acc[i][v] = to_float(direct[(size_t)t * ldi + (size_t)(h0 + i) * D + d + v]);
+        } else {
+            const int ci = nvh > 1 ? c : 0;
+            // without talk, head h needs only its own result
+            const int q_lo = talk != nullptr ? 0 : h0, q_hi = talk != nullptr ? H : h0 + nh;
+            for (int q = q_lo; q < q_hi; ++q) {
+                const size_t pi = ((size_t)t * H + q) * nvh + ci;
+                float p[VEC];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) p[v] = 0.f;
+                if (pair_ml != nullptr) {
+                    for (int sp = 0; sp < splits; ++sp) {
+                        const float f = factor[(q * nvh + ci) * splits + sp];
+                        const float* src = pairs + (pi * splits + sp) * D + d;
+                        if constexpr (VEC == 4) {
+                            const float4 x = *reinterpret_cast<const float4*>(src);
+                            p[0] += f * x.x; p[1] += f * x.y; p[2] += f * x.z; p[3] += f * x.w;
+                        } else {
+                            p[0] += f * src[0];
+                        }
+                    }
+                } else {
+                    const float* src = pairs + pi * D + d;
+                    if constexpr (VEC == 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(src);
+                        p[0] = x.x; p[1] = x.y; p[2] = x.z; p[3] = x.w;
+                    } else {
+                        p[0] = src[0];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < MIX_HEADS; ++i) {
+                    const float w = talk != nullptr ? (i < nh ? talk_s[(h0 + i) * H + q] : 0.f)
+                                                    : (h0 + i == q ? 1.f : 0.f);
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[i][v] = fmaf(w, p[v], acc[i][v]);
+                }
             }
         }
-    } else {
-        v = to_float(direct[(size_t)t * ldi + idx]);
+#pragma unroll
+        for (int i = 0; i < MIX_HEADS; ++i) {
+            if (i >= nh) break;
+            const size_t col = (size_t)(h0 + i) * D + d;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                float r = acc[i][v];
+                if (gate != nullptr) r *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * ldg + col + v])));
+                out[(size_t)t * ldo + col + v] = from_float<T>(r);
+            }
+        }
     }
-    if (gate != nullptr) v *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * ldg + idx])));
-    out[(size_t)t * ldo + idx] = from_float<T>(v);
 }
 
 template <typename T>
@@ -291,10 +343,18 @@ static int launch_mix(const float* pairs, const float* pair_ml, int splits, int 
     if (pairs != nullptr && ((nvh != 1 && nvh != Hkv) || (talk != nullptr && nvh != Hkv && Hkv != 1)))
         return SLB_ERR_BAD_ARG;
     if (pair_ml != nullptr && (pairs == nullptr || splits < 1)) return SLB_ERR_BAD_ARG;
-    const size_t smem = pair_ml != nullptr ? (size_t)H * nvh * splits * sizeof(float) : 0;
+    const size_t smem = ((talk != nullptr ? (size_t)H * H : 0) +
+                         (pair_ml != nullptr ? (size_t)H * nvh * splits : 0)) * sizeof(float);
     if (smem > 48 * 1024) return SLB_ERR_TOO_LARGE;
-    return slb_launch(mix_heads_gate_kernel<T>, dim3((H * D + 255) / 256, T_tokens), dim3(256), smem, st,
-                      pairs, pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
+    const bool vec = D % 4 == 0 && ((uintptr_t)pairs & 15) == 0 && pairs != nullptr;
+    const int work = Hkv * (vec ? D / 4 : D);
+    const int threads = work >= 256 ? 256 : (work + 31) / 32 * 32;
+    const dim3 grid((work + threads - 1) / threads, T_tokens);
+    if (vec)
+        return slb_launch(mix_heads_gate_kernel<T, 4>, grid, dim3(threads), smem, st, pairs, pair_ml, splits,
+                          nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
+    return slb_launch(mix_heads_gate_kernel<T, 1>, grid, dim3(threads), smem, st, pairs, pair_ml, splits, nvh,
+                      direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
 }
 
 extern "C" {

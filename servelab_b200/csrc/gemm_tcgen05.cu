@@ -434,7 +434,13 @@ __global__ void gemm_tc_reduce_kernel(const float* __restrict__ partial, TO* __r
 //              the tile's 128 updated values.  The product that consumes z multiplies its result
 //              by rstd[tok] = 1 / sqrt(sum over tiles of sumsq / N + eps) in its epilogue
 //              (RowScale), because W (z rstd) = rstd (W z).
-enum { EPI_STORE = 0, EPI_ROPE = 1, EPI_RESID = 2 };
+//              Dynamic Tanh mode (post_alpha not null), for norms that reduce nothing over the
+//              row: d = tanh(*post_alpha * sum) * post_w[n] + post_b[n] is what is added to the
+//              stream (the norm on the branch's result), and z[tok, n] = bfloat16(tanh(*pre_alpha *
+//              resid[tok, n]) * norm_weight[n] + pre_b[n]) is the finished normed row of the next
+//              sublayer; no sums of squares are written and the consumer applies no factor.
+enum { EPI_STORE = 0, EPI_ROPE = 1, EPI_RESID = 2, EPI_DYT = 3 };      // EPI_DYT: EPI_RESID in Dynamic Tanh mode
+#define EPI_IS_RESID(e) ((e) == EPI_RESID || (e) == EPI_DYT)
 
 struct ResidEpilogue {
     float* resid;                       // [M][ld] float32, updated in place
@@ -442,7 +448,12 @@ struct ResidEpilogue {
     const float* norm_weight;           // [N]
     bf16* z;                            // [M][ldz]
     int ldz;
-    float* sumsq;                       // [M][row tiles]
+    float* sumsq;                       // [M][row tiles]; null in Dynamic Tanh mode
+    const float* post_alpha;            // Dynamic Tanh mode: scalars on the device, vectors [N]
+    const float* post_w;
+    const float* post_b;
+    const float* pre_alpha;
+    const float* pre_b;
 };
 
 
@@ -568,10 +579,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             rope.seq_of_token += tok_base;
             rope.q_out += (size_t)tok_base * rope.ld_q;
         }
-        if (EPI == EPI_RESID) {
+        if (EPI_IS_RESID(EPI)) {
             res.resid += (size_t)tok_base * res.ld;
             res.z += (size_t)tok_base * res.ldz;
-            res.sumsq += (size_t)tok_base * gridDim.x;
+            if (res.sumsq != nullptr) res.sumsq += (size_t)tok_base * gridDim.x;
         }
         if (rs.sumsq != nullptr) rs.sumsq += (size_t)tok_base * rs.tiles;
     }
@@ -627,13 +638,19 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
     RopeTarget first_target = {};                            // EPI_ROPE: for token `rank` of this block
     float first_sn[2][4] = {}, first_cs[2][4] = {};          // EPI_ROPE, WIDE: of this warp's first two tokens
     float resid_ahead0 = 0.f, resid_ahead1 = 0.f, norm_w = 0.f, bias_n = 0.f;   // EPI_RESID: fetched while the main loop runs
+    float dy_pw = 0.f, dy_pb = 0.f, dy_b = 0.f, dy_pa = 0.f, dy_a = 0.f;        // EPI_RESID, Dynamic Tanh mode
+    constexpr bool dyt = EPI == EPI_DYT;
+    if (dyt) {                                                                  // (weights: before the wait)
+        dy_pa = *res.post_alpha;
+        dy_a = *res.pre_alpha;
+    }
     // The q|k|v product of a step of few tokens lets its successor, the attention, be scheduled at
     // once: its blocks then look up their pages and request the keys of earlier steps while this
     // product's main loop runs (2.80 -> 2.77 ms a batch-8 step of the 7B shape, 2.66 -> 2.64 at batch
     // 1; from 32 tokens on the same cost 0.02 to 0.05 ms, so the many-token form does not do it).
     if ((flags & SLB_FLAG_PDL_EARLY) || (EPI == EPI_ROPE && !WIDE)) pdl_launch_dependents();
     const bool tracer = threadIdx.x == 64;                  // lane 0 of the first epilogue warp
-    constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : (EPI == EPI_RESID ? 7 : 2);
+    constexpr int TRACE_ID = EPI == EPI_ROPE ? 3 : (EPI_IS_RESID(EPI) ? 7 : 2);
     if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_START);
 
     if (warp == 0) {
@@ -733,12 +750,17 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
         pdl_wait();
         if (tracer) slb_trace_event(tr, TRACE_ID, SLB_TR_WAITED);
         if (rs.sumsq != nullptr) rows_rstd(rs, M, quarter, lane, rstd_s);   // in the shadow of the main loop
-        if constexpr (EPI == EPI_RESID && !WIDE) {
+        if constexpr (EPI_IS_RESID(EPI) && !WIDE) {
             // what this thread's column needs of the first two tokens of this block's share
             const int tok0 = (int)cluster_rank(), tok1 = tok0 + (int)cluster_size();
             if (n0 + row < N) {
                 norm_w = res.norm_weight[n0 + row];
                 if (bias) bias_n = bias[n0 + row];
+                if (dyt) {
+                    dy_pw = res.post_w[n0 + row];
+                    dy_pb = res.post_b[n0 + row];
+                    dy_b = res.pre_b[n0 + row];
+                }
                 if (tok0 < M) resid_ahead0 = __ldcg(res.resid + (size_t)tok0 * res.ld + n0 + row);
                 if (tok1 < M) resid_ahead1 = __ldcg(res.resid + (size_t)tok1 * res.ld + n0 + row);
             }
@@ -783,7 +805,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             // what a lane reads and writes of a row is 8- or 16-byte aligned)
             const int w4 = warp & 3, r4 = 4 * lane, n4 = n0 + r4;
             const bool in = n4 < N;
-            float4 nw = make_float4(0.f, 0.f, 0.f, 0.f), bs = nw, fr = nw;
+            float4 nw = make_float4(0.f, 0.f, 0.f, 0.f), bs = nw, fr = nw, dpw = nw, dpb = nw, dbb = nw;
             // the q|k|v form: where this lane's rows lie (the same for every token)
             int rope_j = 0, rope_e0 = 0, partner = lane;
             bool rotate = false, first_half = true, is_v = false;
@@ -802,8 +824,13 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 }
                 if (in && rope.bias) bs = *reinterpret_cast<const float4*>(rope.bias + n4);
             } else if (in) {
-                if (EPI == EPI_RESID) nw = *reinterpret_cast<const float4*>(res.norm_weight + n4);
+                if (EPI_IS_RESID(EPI)) nw = *reinterpret_cast<const float4*>(res.norm_weight + n4);
                 if (bias) bs = *reinterpret_cast<const float4*>(bias + n4);
+                if (dyt) {
+                    dpw = *reinterpret_cast<const float4*>(res.post_w + n4);
+                    dpb = *reinterpret_cast<const float4*>(res.post_b + n4);
+                    dbb = *reinterpret_cast<const float4*>(res.pre_b + n4);
+                }
             }
             // what is left to do for a token once its sums v[0..3] (rows r4 .. r4 + 3) exist
             auto finish = [&](int tok, float (&v)[4], const float (&before)[4], bool first_turn, int u) {
@@ -816,22 +843,29 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
                 for (int c = 0; c < 4; ++c) v[c] += (&bs.x)[c];
                 if constexpr (EPI == EPI_STORE) {
                     if (in) store4_bf16(out + (size_t)tok * ldo + n4, v);
-                } else if constexpr (EPI == EPI_RESID) {
+                } else if constexpr (EPI_IS_RESID(EPI)) {
                     float sq = 0.f;
                     if (in) {
                         float r[4], zv[4];
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            r[c] = before[c] + v[c];
-                            zv[c] = r[c] * (&nw.x)[c];
-                            sq += r[c] * r[c];
+                            if (dyt) {
+                                r[c] = before[c] + (tanhf(dy_pa * v[c]) * (&dpw.x)[c] + (&dpb.x)[c]);
+                                zv[c] = tanhf(dy_a * r[c]) * (&nw.x)[c] + (&dbb.x)[c];
+                            } else {
+                                r[c] = before[c] + v[c];
+                                zv[c] = r[c] * (&nw.x)[c];
+                                sq += r[c] * r[c];
+                            }
                         }
                         *reinterpret_cast<float4*>(res.resid + (size_t)tok * res.ld + n4) =
                             make_float4(r[0], r[1], r[2], r[3]);
                         store4_bf16(res.z + (size_t)tok * res.ldz + n4, zv);
                     }
-                    sq = warp_sum(sq);
-                    if (lane == 0) res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] = sq;
+                    if (!dyt) {
+                        sq = warp_sum(sq);
+                        if (lane == 0) res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] = sq;
+                    }
                 } else {
                     float other[4];
 #pragma unroll
@@ -876,7 +910,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
 #pragma unroll
                     for (uint32_t p = 0; p < (uint32_t)TC_MAX_CLUSTER; ++p)
                         part[u][p] = (live && p < nranks) ? ld_peer_f32x4(addr, p) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    if constexpr (EPI == EPI_RESID)
+                    if constexpr (EPI_IS_RESID(EPI))
                         if (live && in) {
                             const float4 b4 = __ldcg(reinterpret_cast<const float4*>(res.resid + (size_t)t * res.ld + n4));
                             before[u][0] = b4.x; before[u][1] = b4.y; before[u][2] = b4.z; before[u][3] = b4.w;
@@ -919,23 +953,31 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_cluster_kernel(
             if (rs.sumsq != nullptr) sum *= rstd_s[tok];
             if constexpr (EPI == EPI_STORE) {
                 if (n < N) out[(size_t)tok * ldo + n] = __float2bfloat16_rn(sum + (bias ? bias[n] : 0.f));
-            } else if constexpr (EPI == EPI_RESID) {
+            } else if constexpr (EPI_IS_RESID(EPI)) {
                 float r = 0.f;
                 if (n < N) {
                     float* dst = res.resid + (size_t)tok * res.ld + n;
                     const float before = turn == 0 ? resid_ahead0 : (turn == 1 ? resid_ahead1 : __ldcg(dst));
-                    r = before + (sum + bias_n);
-                    *dst = r;
-                    res.z[(size_t)tok * res.ldz + n] = __float2bfloat16_rn(r * norm_w);
+                    if (dyt) {
+                        r = before + (tanhf(dy_pa * (sum + bias_n)) * dy_pw + dy_pb);
+                        *dst = r;
+                        res.z[(size_t)tok * res.ldz + n] = __float2bfloat16_rn(tanhf(dy_a * r) * norm_w + dy_b);
+                    } else {
+                        r = before + (sum + bias_n);
+                        *dst = r;
+                        res.z[(size_t)tok * res.ldz + n] = __float2bfloat16_rn(r * norm_w);
+                    }
                 }
                 ++turn;
-                const float sq = warp_sum(r * r);
-                if (lane == 0) warp_sq[parity][warp & 3] = sq;
-                asm volatile("bar.sync 1, 128;" ::: "memory");           // the four epilogue warps
-                if (row == 0)
-                    res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] =
-                        ((warp_sq[parity][0] + warp_sq[parity][1]) + warp_sq[parity][2]) + warp_sq[parity][3];
-                parity ^= 1;
+                if (!dyt) {                                              // (uniform over the block)
+                    const float sq = warp_sum(r * r);
+                    if (lane == 0) warp_sq[parity][warp & 3] = sq;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps
+                    if (row == 0)
+                        res.sumsq[(size_t)tok * gridDim.x + blockIdx.x] =
+                            ((warp_sq[parity][0] + warp_sq[parity][1]) + warp_sq[parity][2]) + warp_sq[parity][3];
+                    parity ^= 1;
+                }
             } else {
                 const RopeTarget t = tok == (int)rank ? first_target
                                                       : rope_target(rope, tok, tok_pos[tok], tok_page[tok], n, row, N);
@@ -1065,7 +1107,7 @@ int run_cluster(const bf16* x, int ldx, const bf16* W, int ldw, bf16* out, int l
     };
     bool wide_ok = N % 4 == 0 && aligned(bias, 0, 4, 16);
     if (EPI == EPI_STORE) wide_ok = wide_ok && aligned(out, ldo, 2, 8);
-    if (EPI == EPI_RESID)
+    if (EPI_IS_RESID(EPI))
         wide_ok = wide_ok && aligned(res.resid, res.ld, 4, 16) && aligned(res.z, res.ldz, 2, 8) &&
                   aligned(res.norm_weight, 0, 4, 16);
     if (EPI == EPI_ROPE)
@@ -1150,8 +1192,29 @@ int slb_gemm_tc_resid_norm_bf16(const bf16* x, int ldx, const bf16* W, int ldw, 
         return SLB_ERR_BAD_ARG;
     const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits, tok_group);
     if (rc != 0) return rc;
-    const ResidEpilogue res = {resid, ld_resid, norm_weight, z, ldz, sumsq};
+    const ResidEpilogue res = {resid, ld_resid, norm_weight, z, ldz, sumsq, nullptr, nullptr, nullptr, nullptr, nullptr};
     return run_cluster<EPI_RESID>(x, ldx, W, ldw, nullptr, 0, bias, M, N, K, splits, max_stages, RopeEpilogue{},
+                                  res, RowScale{}, tok_group, st);
+}
+
+// The same product closing a branch of a block whose norms are Dynamic Tanh:
+//   resid (float32, in place) += tanh(*post_alpha * (x . W^T)) * post_w + post_b
+//   z = bfloat16(tanh(*pre_alpha * resid) * pre_w + pre_b)
+// z is the finished normed row; the scalars are read on the device.
+int slb_gemm_tc_resid_dyt_bf16(const bf16* x, int ldx, const bf16* W, int ldw, float* resid, int ld_resid,
+                               const float* post_alpha, const float* post_w, const float* post_b,
+                               const float* pre_alpha, const float* pre_w, const float* pre_b, bf16* z,
+                               int ldz, int M, int N, int K, int splits, int max_stages, int tok_group,
+                               cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (resid == nullptr || z == nullptr || ld_resid < N || ldz < N || post_alpha == nullptr ||
+        post_w == nullptr || post_b == nullptr || pre_alpha == nullptr || pre_w == nullptr || pre_b == nullptr)
+        return SLB_ERR_BAD_ARG;
+    if (((uintptr_t)post_w | (uintptr_t)post_b | (uintptr_t)pre_b) % 16) return SLB_ERR_BAD_ARG;
+    const int rc = check_cluster_args(x, ldx, W, ldw, M, N, K, splits, tok_group);
+    if (rc != 0) return rc;
+    const ResidEpilogue res = {resid, ld_resid, pre_w, z, ldz, nullptr, post_alpha, post_w, post_b, pre_alpha, pre_b};
+    return run_cluster<EPI_DYT>(x, ldx, W, ldw, nullptr, 0, nullptr, M, N, K, splits, max_stages, RopeEpilogue{},
                                   res, RowScale{}, tok_group, st);
 }
 

@@ -3,9 +3,9 @@
 //
 // Input is the fused projection of each token, [T, C] with C = H D query channels followed
 // by Hkv D key channels (more columns may follow; they are not touched).  Per channel c and
-// token t at index j of its request's portion:
+// token t at index j of its request's portion (the taps are passed transposed, w[i][c]):
 //
-//   y_t = sum_i w[c][i] * u_(j - (taps - 1) + i)
+//   y_t = sum_i w[i][c] * u_(j - (taps - 1) + i)
 //
 // where u comes from the portion for indices >= 0 and from the request's state record for
 // the taps - 1 rows before it: state[slot][i][c] is the projected row taps - 1 - i places
@@ -24,7 +24,49 @@
 
 SLB_DEFINE_STATUS_WORD(conv_cache_status_word, slb_conv_cache_status)
 
-template <typename T>
+// VEC consecutive elements as floats, by 16-byte accesses where VEC allows
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&v)[VEC]) {
+    if constexpr (VEC == 1) {
+        v[0] = to_float(p[0]);
+    } else if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(p + i);
+            v[i] = x.x; v[i + 1] = x.y; v[i + 2] = x.z; v[i + 3] = x.w;
+        }
+    } else {
+        static_assert(VEC == 8, "bfloat16 vectors are 8 wide");
+        const uint4 x = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 1) {
+        p[0] = from_float<T>(v[0]);
+    } else if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4)
+            *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    } else {
+        uint4 x;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = x;
+    }
+}
+
+// taps_w is [taps][C] (a tap's weights of neighbouring channels are neighbours).  A thread owns
+// VEC neighbouring channels of one token; a vector never straddles the q | k border or a head.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
     const T* __restrict__ proj, int ldp, const float* __restrict__ taps_w, int taps,
     float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_q,
@@ -33,12 +75,7 @@ __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
     float temp_coef, int temp_every, T* __restrict__ q_out, int ldq, T* __restrict__ k_cache,
     int q_size, int Hkv, int D, int update_inline) {
     const int C = q_size + Hkv * D;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    float w[SC_MAX_TAPS];
-    if (c < C) {
-#pragma unroll
-        for (int i = 0; i < SC_MAX_TAPS; ++i) w[i] = i < taps ? taps_w[(size_t)c * taps + i] : 0.f;
-    }
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     pdl_launch_dependents();
     pdl_wait();
     if (c >= C) return;
@@ -49,29 +86,41 @@ __global__ void __launch_bounds__(256) qk_conv_cache_kernel(
     const int pos = positions[t];
     const int hist = taps - 1;
     float* st = state != nullptr ? state + (size_t)state_slots[s] * hist * C + c : nullptr;
-    float y = 0.f;
+    float y[VEC];
 #pragma unroll
-    for (int i = 0; i < SC_MAX_TAPS; ++i) {
-        if (i < taps) {
-            const int jj = j - hist + i;
-            float u;
-            if (jj >= 0) u = to_float(proj[(size_t)(q0 + jj) * ldp + c]);
-            else u = st != nullptr ? st[(size_t)(hist + jj) * C] : 0.f;
-            y += w[i] * u;
-            // a step of single tokens: row i of the new record is row i + 1 of (record, token)
-            if (update_inline && i >= 1 && st != nullptr) st[(size_t)(i - 1) * C] = u;
+    for (int v = 0; v < VEC; ++v) y[v] = 0.f;
+    for (int i = 0; i < taps; ++i) {
+        const int jj = j - hist + i;
+        float u[VEC], w[VEC];
+        if (jj >= 0) {
+            load_vec<T, VEC>(proj + (size_t)(q0 + jj) * ldp + c, u);
+        } else if (st != nullptr) {
+            load_vec<float, VEC>(st + (size_t)(hist + jj) * C, u);
+        } else {
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) u[v] = 0.f;
         }
+        load_vec<float, VEC>(taps_w + (size_t)i * C + c, w);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) y[v] = fmaf(w[v], u[v], y[v]);
+        // a step of single tokens: row i - 1 of the new record is row i of (record, token); this
+        // thread alone reads and writes these columns of the record, in this order
+        if (update_inline && i >= 1 && st != nullptr) store_vec<float, VEC>(st + (size_t)(i - 1) * C, u);
     }
     if (c < q_size) {
-        if (temp_coef != 0.f) y *= 1.f + temp_coef * logf(floorf((float)(pos + 1) / (float)temp_every) + 1.f);
-        q_out[(size_t)t * ldq + c] = from_float<T>(y);
+        if (temp_coef != 0.f) {
+            const float f = 1.f + temp_coef * logf(floorf((float)(pos + 1) / (float)temp_every) + 1.f);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) y[v] *= f;
+        }
+        store_vec<T, VEC>(q_out + (size_t)t * ldq + c, y);
     } else if (k_cache != nullptr) {
         const int cc = c - q_size;
         const int kvh = cc / D, d = cc - kvh * D;
         const int page = block_table[(size_t)s * max_pages + pos / page_size];
         if (page >= num_pages) atomicCAS(&conv_cache_status_word, 0, 1);
         else if (page >= 0)
-            k_cache[(((size_t)page * Hkv + kvh) * page_size + pos % page_size) * D + d] = from_float<T>(y);
+            store_vec<T, VEC>(k_cache + (((size_t)page * Hkv + kvh) * page_size + pos % page_size) * D + d, y);
     }
 }
 
@@ -108,11 +157,24 @@ static int launch_conv(const T* proj, int ldp, const float* taps_w, int taps, fl
         return SLB_ERR_BAD_ARG;
     if (taps > SC_MAX_TAPS) return SLB_ERR_TOO_LARGE;
     const int C = q_size + Hkv * D;
-    const dim3 grid((C + 255) / 256, T_tokens);
     const int inline_update = decode_only && taps > 1 ? 1 : 0;
-    int rc = slb_launch(qk_conv_cache_kernel<T>, grid, dim3(256), 0, st, proj, ldp, taps_w, taps, state,
-                        state_slots, cu_q, seq_of_token, positions, block_table, max_pages, page_size,
-                        num_pages, temp_coef, temp_every, q_out, ldq, k_cache, q_size, Hkv, D, inline_update);
+    constexpr int V = 16 / (int)sizeof(T);             // channels of one 16-byte access
+    const bool vec = q_size % V == 0 && D % V == 0 && ldp % V == 0 && ldq % V == 0 && C % 4 == 0 &&
+                     (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)state |
+                       (uintptr_t)taps_w) & 15) == 0;
+    int rc;
+    if (vec) {
+        const int threads = C / V >= 256 ? 256 : 64;
+        rc = slb_launch(qk_conv_cache_kernel<T, V>, dim3((C / V + threads - 1) / threads, T_tokens), dim3(threads),
+                        0, st, proj, ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions,
+                        block_table, max_pages, page_size, num_pages, temp_coef, temp_every, q_out, ldq,
+                        k_cache, q_size, Hkv, D, inline_update);
+    } else {
+        rc = slb_launch(qk_conv_cache_kernel<T, 1>, dim3((C + 255) / 256, T_tokens), dim3(256), 0, st, proj,
+                        ldp, taps_w, taps, state, state_slots, cu_q, seq_of_token, positions, block_table,
+                        max_pages, page_size, num_pages, temp_coef, temp_every, q_out, ldq, k_cache, q_size,
+                        Hkv, D, inline_update);
+    }
     if (rc != 0 || taps == 1 || inline_update) return rc;
     return slb_launch(conv_state_update_kernel<T>, dim3((C + 255) / 256, S), dim3(256), 0, st, proj, ldp,
                       taps, state, state_slots, cu_q, C);

@@ -331,13 +331,13 @@ def qk_conv_cache(proj: torch.Tensor, taps_w: torch.Tensor, state: Optional[torc
                   block_table: torch.Tensor, page_size: int, temp_coef: float, temp_every: int,
                   q_out: torch.Tensor, k_cache: Optional[torch.Tensor], num_kv_heads: int,
                   head_dim: int) -> None:
-    """Causal convolution over time (``taps_w`` float32 [C, taps]) on the first C = q width +
+    """Causal convolution over time (``taps_w`` float32 [taps, C]: transposed) on the first C = q width +
     kv width columns of ``proj``, with the rows before a portion taken from ``state``
     (float32 [slots, taps - 1, C], indexed by ``ctx.state_slots`` and updated); queries times
     their temperature into ``q_out``, keys into the pages of ``k_cache`` (None: not written)."""
     fn = getattr(L.core(), "slb_qk_conv_cache_" + _suffix(proj.dtype))
-    n = 1 if (taps_w.shape[1] == 1 or ctx.decode_only) else 2
-    L.check(fn(proj.data_ptr(), proj.stride(0), taps_w.data_ptr(), taps_w.shape[1], _p(state),
+    n = 1 if (taps_w.shape[0] == 1 or ctx.decode_only) else 2
+    L.check(fn(proj.data_ptr(), proj.stride(0), taps_w.data_ptr(), taps_w.shape[0], _p(state),
                ctx.state_slots.data_ptr(), ctx.cu_q.data_ptr(), ctx.seq_of_token.data_ptr(),
                ctx.positions.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
                _num_pages(k_cache), float(temp_coef), int(temp_every), q_out.data_ptr(), q_out.stride(0),
@@ -779,6 +779,25 @@ def gemm_tc_resid_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
         M, N, Kd, splits, _cluster_stages(M, groups), tc_token_group if groups > 1 else 0,
         _stream()), "gemm_tc_resid_norm")
     return ScaledRows(z, sumsq, eps, resid, norm_weight)
+
+
+def gemm_tc_resid_dyt(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, post, pre,
+                      splits: int = 0) -> torch.Tensor:
+    """The product that closes a residual branch of a block with Dynamic Tanh norms, in one
+    kernel: resid (float32, in place) += post(x . w^T); returns pre(resid) in bfloat16, the
+    finished normed rows.  ``post`` / ``pre`` are (alpha, weight, bias) float32 device tensors.
+    Up to 64 tokens."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    groups = tc_token_groups(M, w)
+    splits = splits or tc_cluster_splits(N, Kd, groups)
+    z = torch.empty((M, N), dtype=_BF16, device=x.device)
+    L.check(L.core().slb_gemm_tc_resid_dyt_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), resid.data_ptr(), resid.stride(0),
+        post[0].data_ptr(), post[1].data_ptr(), post[2].data_ptr(), pre[0].data_ptr(), pre[1].data_ptr(),
+        pre[2].data_ptr(), z.data_ptr(), z.stride(0), M, N, Kd, splits, _cluster_stages(M, groups),
+        tc_token_group if groups > 1 else 0, _stream()), "gemm_tc_resid_dyt")
+    return z
 
 
 def gemm_tc_status(reset: bool = False) -> int:

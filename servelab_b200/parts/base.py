@@ -107,6 +107,11 @@ class Norm(Part):
     def forward(self, ctx, resid, delta, out_rows=None) -> torch.Tensor:
         raise NotImplementedError
 
+    def apply(self, ctx, x) -> torch.Tensor:
+        """The norm of ``x`` [T, dim] alone (no stream to add into), in the compute dtype: what
+        a block needs that norms a sublayer's result before adding it."""
+        return self.forward(ctx, x.to(torch.float32), None)
+
 
 class Mixer(Part):
     @classmethod

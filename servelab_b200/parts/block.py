@@ -108,10 +108,11 @@ class SandwichNormBlock(PreNormBlock):
 
     def forward(self, ctx, resid, delta, cache, owns_cache):
         x = self.mixer_norm.forward(ctx, resid, plain_unless(self.mixer_norm, delta))
-        a = plain_unless(None, self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache))
+        # (a sublayer's result may be a product not launched yet, if its pending norm takes that)
+        a = plain_unless(self.mixer_post_norm, self.mixer.forward(ctx, plain_unless(self.mixer, x), cache, owns_cache))
         a = PostNormed(ctx, a, self.mixer_post_norm)
         if self.feed_forward is None:
             return resid, a
         x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
-        f = plain_unless(None, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x)))
+        f = plain_unless(self.ff_post_norm, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x)))
         return resid, PostNormed(ctx, f, self.ff_post_norm)

@@ -92,9 +92,10 @@ class ConvTalkAttention(Mixer):
         self.w_in = store.cat([n["q"], n["k"]] + ([n["gate"]] if s.output_gate else []))
         self.w_o = store.get(n["o"])
         if s.conv_taps > 1:
-            self.taps = store.cat([n["q"] + s.conv_suffix, n["k"] + s.conv_suffix])
+            # [taps, channels]: a tap's weights of neighbouring channels are neighbours
+            self.taps = store.cat([n["q"] + s.conv_suffix, n["k"] + s.conv_suffix]).t().contiguous()
         else:
-            self.taps = torch.ones((self.q_size + self.kv_size, 1), dtype=torch.float32,
+            self.taps = torch.ones((1, self.q_size + self.kv_size), dtype=torch.float32,
                                    device=self.env.device)
         self.r1 = store.get(f"{self.prefix}.{s.bias_r1_name}") if s.distance_bias else None
         self.r2 = store.get(f"{self.prefix}.{s.bias_r2_name}") if s.distance_bias else None
@@ -114,4 +115,4 @@ class ConvTalkAttention(Mixer):
         out = torch.empty_like(q)
         A.talk_attention(ctx, q, cache.k, cache.v, out, table, s.num_heads, s.num_kv_heads, s.head_dim,
                          cache.page_size, self.scale, s.window or 0, self.r1, self.r2, self.talk, gate)
-        return linear(out, self.w_o)
+        return linear(out, self.w_o, consumer="norm")

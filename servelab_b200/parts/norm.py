@@ -41,6 +41,9 @@ class RMSNorm(Norm):
         return out
 
 
+fuse_product_norms = True     # Dynamic Tanh: a deferred product runs with the norms in its epilogue
+
+
 class PostNormed:
     """A sublayer's result that still lacks the norm it must pass before it is added to the
     stream (the "b" norm of a sandwich block): the next norm kernel applies that norm, the add
@@ -57,7 +60,7 @@ class PostNormed:
         return self.value.shape
 
     def materialize(self) -> torch.Tensor:
-        return self.norm.apply(self.ctx, self.value)
+        return self.norm.apply(self.ctx, K.plain_unless(None, self.value))
 
 
 @register_norm("dynamic_tanh")
@@ -67,6 +70,9 @@ class DynamicTanh(Norm):
     one kernel then norms the update, adds it and norms the sum."""
     graph_safe = True
     accepts_post_normed = True
+    accepts_deferred_linear = True    # as the pending norm of a PostNormed value: the value may be a
+                                      # product not launched yet, which then runs with both norms
+                                      # and the add in its epilogue
 
     @classmethod
     def declare(cls, spec, prefix):
@@ -86,8 +92,15 @@ class DynamicTanh(Norm):
         if isinstance(delta, PostNormed):
             if isinstance(delta.norm, DynamicTanh):
                 post, delta = delta.norm.params, delta.value
+                if isinstance(delta, K.DeferredLinear):
+                    if (out_rows is None and self.env.dtype == torch.bfloat16 and delta.bias is None
+                            and fuse_product_norms):
+                        return K.gemm_tc_resid_dyt(delta.x, delta.w, resid, post, self.params)
+                    delta = delta.materialize()
             else:
                 delta = delta.materialize()
+        elif isinstance(delta, K.DeferredLinear):
+            delta = delta.materialize()
         rows = resid.shape[0] if out_rows is None else out_rows.numel()
         out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
         K.dyt_add_norm(resid, delta, post, self.params, out, out_rows)

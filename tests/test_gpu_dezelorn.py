@@ -60,20 +60,47 @@ def test_dynamic_tanh_kernel(dtype, dim):
     assert (r3.cpu().double() - (resid.double() + delta.double())).abs().max() < 1e-6
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 40])
+def test_product_with_both_norms_in_its_epilogue(M):
+    """The product that closes a branch, the Dynamic Tanh of its result, the add and the Dynamic
+    Tanh of the next sublayer's input in one kernel, against the oracle; one row of the stream
+    a thousand times larger than the others."""
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(M)
+    N, Kd = 384, 1024
+    x = (torch.randn(M, Kd, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, Kd, generator=g) * 0.05).bfloat16()
+    resid = torch.randn(M, N, generator=g)
+    resid[M // 2] *= 1000.0
+    post = (torch.tensor([0.8]), torch.randn(N, generator=g), torch.randn(N, generator=g))
+    pre = (torch.tensor([0.3]), torch.randn(N, generator=g), torch.randn(N, generator=g))
+    prod = x.double() @ w.double().T
+    want_resid = resid.double() + plain.dynamic_tanh(prod, post[1].double(), post[2].double(), 0.8)
+    want_z = plain.dynamic_tanh(want_resid, pre[1].double(), pre[2].double(), 0.3)
+    r = resid.to(DEV)
+    z = K.gemm_tc_resid_dyt(x.to(DEV), w.to(DEV), r, tuple(t.to(DEV) for t in post),
+                            tuple(t.to(DEV) for t in pre))
+    assert K.gemm_tc_status() == 0
+    assert ((r.cpu().double() - want_resid).abs() / (1 + want_resid.abs())).max() < 2e-3
+    assert (z.cpu().double() - want_z).abs().max() < 3e-2
+
+
 # ----------------------------------------------------- convolution + cache
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [8, 6])
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
-def test_conv_kernel_over_portions_and_single_tokens(dtype, taps):
+def test_conv_kernel_over_portions_and_single_tokens(dtype, taps, D):
     """Two requests fed in unequal portions (one of them of single tokens from the start, so
     the state is shifted on the spot) give the convolution of their whole sequences; keys land
     in the pages the tables name; the extra columns of the projection are not touched."""
     from servelab_b200.ops import kernels as K
-    H_, Hkv, D, ps, pages = 3, 2, 8, 4, 24
+    H_, Hkv, ps, pages = 3, 2, 4, 24           # (head size 6: no 16-byte vectors, the scalar instance)
     qs, kv = H_ * D, Hkv * D
     Cw = qs + kv
     g = torch.Generator().manual_seed(taps)
     lens = {"a": 23, "b": 9}
-    proj = {r: torch.randn(n, Cw + 5, generator=g).to(dtype) for r, n in lens.items()}
+    extra = 8 if D == 8 else 5                 # (rows stay 16-byte aligned for head size 8)
+    proj = {r: torch.randn(n, Cw + extra, generator=g).to(dtype) for r, n in lens.items()}
     w = torch.randn(Cw, taps, generator=g)
     state = torch.zeros(4, max(taps - 1, 1), Cw, device=DEV) if taps > 1 else None
     kc = torch.zeros(pages, Hkv, ps, D, dtype=dtype, device=DEV)
@@ -93,7 +120,7 @@ def test_conv_kernel_over_portions_and_single_tokens(dtype, taps):
         ctx = _ctx(ents)
         x = torch.cat(chunks).to(DEV)
         q = torch.full((x.shape[0], qs), 7.0, dtype=dtype, device=DEV)
-        K.qk_conv_cache(x, w.to(DEV), state, ctx, ctx.block_tables[0], ps, coef, every, q, kc, Hkv, D)
+        K.qk_conv_cache(x, w.t().contiguous().to(DEV), state, ctx, ctx.block_tables[0], ps, coef, every, q, kc, Hkv, D)
         assert torch.equal(x.cpu(), torch.cat(chunks))
         off = 0
         for r, n in step.items():
