@@ -231,13 +231,129 @@ static int launch_generic(const T* q, int ldq, const T* kc, const T* vc, T* out,
 // maxima (base-2 domain) and sums in pair_ml[t][g][c][split][2]: the splits are combined here,
 // weight 2^(m_split - M) / L each.  `pairs` may be null: then `direct` [T, H D] (type T) is the
 // attention's plain result and only the gate is applied; `talk` and `gate` may each be null.
-// A thread owns one value head c and VEC neighbouring columns d, reads pairs[t][g][c][d] once for
-// every query head g and finishes, MIX_HEADS at a time, the heads of group c from it (the
-// [H, H] matrix sits in shared memory).
-#define MIX_HEADS 8
+// A block owns one token and one kv head c, whose group of query heads it finishes MIX_HEADS at
+// a time.  A thread owns VEC neighbouring columns d and a slice of the source heads q: it reads
+// pairs[t][q][c][d] once per q of its slice (combining the splits), multiplies by the mixing
+// weights of the heads being finished, and the slices are added up through shared memory -- a
+// step of few tokens has little work, and many short chains of loads finish sooner than few
+// long ones.
+#define MIX_HEADS 4
+#define MIX_THREADS 256
+#define MIX_ROWS_FROM 64             // above this many tokens the unsliced kernel below runs
 
 template <typename T, int VEC>
-__global__ void __launch_bounds__(256) mix_heads_gate_kernel(
+__global__ void __launch_bounds__(MIX_THREADS) mix_heads_gate_kernel(
+    const float* __restrict__ pairs, const float* __restrict__ pair_ml, int splits, int nvh,
+    const T* direct, int ldi, const float* __restrict__ talk, const T* __restrict__ gate, int ldg,
+    T* out, int ldo, int H, int Hkv, int D) {
+    extern __shared__ float mix_smem[];
+    const int dv = D / VEC;                        // column groups
+    const int slices = max(1, min(MIX_THREADS / dv, H));
+    float* red = mix_smem;                         // [slices][MIX_HEADS][D]
+    float* talk_s = red + slices * MIX_HEADS * D;  // [H][H] (with talk)
+    float* factor = talk_s + (talk != nullptr ? H * H : 0);     // [H][nvh][splits] (with pair_ml)
+    if (talk != nullptr)
+        for (int i = threadIdx.x; i < H * H; i += blockDim.x) talk_s[i] = talk[i];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y, c = blockIdx.x;
+    const int ci = nvh > 1 ? c : 0;
+    if (pair_ml != nullptr) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {          // (q, ci) of every source head
+            const float* ml = pair_ml + (((size_t)t * H + i) * nvh + ci) * splits * 2;
+            float M = -INFINITY;
+            for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, ml[2 * sp]);
+            float L = 0.f;
+            for (int sp = 0; sp < splits; ++sp)
+                if (ml[2 * sp] != -INFINITY) L += ml[2 * sp + 1] * exp2f(ml[2 * sp] - M);
+            for (int sp = 0; sp < splits; ++sp)
+                factor[i * splits + sp] = (L > 0.f && ml[2 * sp] != -INFINITY) ? exp2f(ml[2 * sp] - M) / L : 0.f;
+        }
+    }
+    __syncthreads();
+    const int g = H / Hkv;
+    const int dcol = threadIdx.x % dv, slice = threadIdx.x / dv;
+    const int d = dcol * VEC;
+    const bool worker = slice < slices;
+    for (int h0 = c * g; h0 < (c + 1) * g; h0 += MIX_HEADS) {
+        const int nh = min(MIX_HEADS, (c + 1) * g - h0);
+        float acc[MIX_HEADS][VEC];
+#pragma unroll
+        for (int i = 0; i < MIX_HEADS; ++i)
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[i][v] = 0.f;
+        if (worker && pairs == nullptr) {
+            if (slice == 0) {
+#pragma unroll
+                for (int i = 0; i < MIX_HEADS; ++i)
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v)
+                        if (i < nh) acc[i][v] = to_float(direct[(size_t)t * ldi + (size_t)(h0 + i) * D + d + v]);
+            }
+        } else if (worker) {
+            // without talk, head h needs only its own result
+            const int q_lo = talk != nullptr ? 0 : h0, q_hi = talk != nullptr ? H : h0 + nh;
+            for (int q = q_lo + slice; q < q_hi; q += slices) {
+                const size_t pi = ((size_t)t * H + q) * nvh + ci;
+                float p[VEC];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) p[v] = 0.f;
+                if (pair_ml != nullptr) {
+#pragma unroll 4
+                    for (int sp = 0; sp < splits; ++sp) {
+                        const float f = factor[q * splits + sp];
+                        const float* src = pairs + (pi * splits + sp) * D + d;
+                        if constexpr (VEC == 4) {
+                            const float4 x = *reinterpret_cast<const float4*>(src);
+                            p[0] += f * x.x; p[1] += f * x.y; p[2] += f * x.z; p[3] += f * x.w;
+                        } else {
+                            p[0] += f * src[0];
+                        }
+                    }
+                } else {
+                    const float* src = pairs + pi * D + d;
+                    if constexpr (VEC == 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(src);
+                        p[0] = x.x; p[1] = x.y; p[2] = x.z; p[3] = x.w;
+                    } else {
+                        p[0] = src[0];
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < MIX_HEADS; ++i) {
+                    const float w = talk != nullptr ? (i < nh ? talk_s[(h0 + i) * H + q] : 0.f)
+                                                    : (h0 + i == q ? 1.f : 0.f);
+#pragma unroll
+                    for (int v = 0; v < VEC; ++v) acc[i][v] = fmaf(w, p[v], acc[i][v]);
+                }
+            }
+        }
+        if (worker) {
+#pragma unroll
+            for (int i = 0; i < MIX_HEADS; ++i)
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) red[(slice * MIX_HEADS + i) * D + d + v] = acc[i][v];
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
+            const int i = idx / D, dd = idx - i * D;
+            float r = 0.f;
+            for (int sl = 0; sl < slices; ++sl) r += red[(sl * MIX_HEADS + i) * D + dd];
+            const size_t col = (size_t)(h0 + i) * D + dd;
+            if (gate != nullptr) r *= 1.f / (1.f + expf(-to_float(gate[(size_t)t * ldg + col])));
+            out[(size_t)t * ldo + col] = from_float<T>(r);
+        }
+        __syncthreads();                           // red is rewritten by the next group of heads
+    }
+}
+
+// The same arithmetic for steps of many tokens, where there is work enough without slicing: a
+// thread owns one kv head c and VEC neighbouring columns d of a token, reads pairs[t][q][c][d] once
+// for every source head q and finishes, MIX_ROW_HEADS at a time, the heads of group c from it.
+#define MIX_ROW_HEADS 8
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) mix_heads_gate_rows_kernel(
     const float* __restrict__ pairs, const float* __restrict__ pair_ml, int splits, int nvh,
     const T* direct, int ldi, const float* __restrict__ talk, const T* __restrict__ gate, int ldg,
     T* out, int ldo, int H, int Hkv, int D) {
@@ -267,16 +383,16 @@ __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= Hkv * dv) return;
     const int c = idx / dv, d = (idx - c * dv) * VEC;       // the kv head whose group is finished, columns
-    for (int h0 = c * g; h0 < (c + 1) * g; h0 += MIX_HEADS) {
-        const int nh = min(MIX_HEADS, (c + 1) * g - h0);
-        float acc[MIX_HEADS][VEC];
+    for (int h0 = c * g; h0 < (c + 1) * g; h0 += MIX_ROW_HEADS) {
+        const int nh = min(MIX_ROW_HEADS, (c + 1) * g - h0);
+        float acc[MIX_ROW_HEADS][VEC];
 #pragma unroll
-        for (int i = 0; i < MIX_HEADS; ++i)
+        for (int i = 0; i < MIX_ROW_HEADS; ++i)
 #pragma unroll
             for (int v = 0; v < VEC; ++v) acc[i][v] = 0.f;
         if (pairs == nullptr) {
 #pragma unroll
-            for (int i = 0; i < MIX_HEADS; ++i)
+            for (int i = 0; i < MIX_ROW_HEADS; ++i)
 #pragma unroll
                 for (int v = 0; v < VEC; ++v)
                     if (i < nh) acc[i][v] = to_float(direct[(size_t)t * ldi + (size_t)(h0 + i) * D + d + v]);
@@ -310,7 +426,7 @@ __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < MIX_HEADS; ++i) {
+                for (int i = 0; i < MIX_ROW_HEADS; ++i) {
                     const float w = talk != nullptr ? (i < nh ? talk_s[(h0 + i) * H + q] : 0.f)
                                                     : (h0 + i == q ? 1.f : 0.f);
 #pragma unroll
@@ -319,7 +435,7 @@ __global__ void __launch_bounds__(256) mix_heads_gate_kernel(
             }
         }
 #pragma unroll
-        for (int i = 0; i < MIX_HEADS; ++i) {
+        for (int i = 0; i < MIX_ROW_HEADS; ++i) {
             if (i >= nh) break;
             const size_t col = (size_t)(h0 + i) * D + d;
 #pragma unroll
@@ -337,23 +453,45 @@ static int launch_mix(const float* pairs, const float* pair_ml, int splits, int 
                       int ldi, const float* talk, const T* gate, int ldg, T* out, int ldo, int T_tokens,
                       int H, int Hkv, int D, cudaStream_t st) {
     if (T_tokens <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || T_tokens > 65535 ||
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || T_tokens > 65535 || Hkv > 65535 ||
         (pairs == nullptr) == (direct == nullptr))
         return SLB_ERR_BAD_ARG;
     if (pairs != nullptr && ((nvh != 1 && nvh != Hkv) || (talk != nullptr && nvh != Hkv && Hkv != 1)))
         return SLB_ERR_BAD_ARG;
     if (pair_ml != nullptr && (pairs == nullptr || splits < 1)) return SLB_ERR_BAD_ARG;
-    const size_t smem = ((talk != nullptr ? (size_t)H * H : 0) +
-                         (pair_ml != nullptr ? (size_t)H * nvh * splits : 0)) * sizeof(float);
-    if (smem > 48 * 1024) return SLB_ERR_TOO_LARGE;
+    if (D > AG_MAX_D) return SLB_ERR_TOO_LARGE;
     const bool vec = D % 4 == 0 && ((uintptr_t)pairs & 15) == 0 && pairs != nullptr;
-    const int work = Hkv * (vec ? D / 4 : D);
-    const int threads = work >= 256 ? 256 : (work + 31) / 32 * 32;
-    const dim3 grid((work + threads - 1) / threads, T_tokens);
-    if (vec)
-        return slb_launch(mix_heads_gate_kernel<T, 4>, grid, dim3(threads), smem, st, pairs, pair_ml, splits,
+    const int dv = vec ? D / 4 : D;
+    if (T_tokens > MIX_ROWS_FROM) {                    // many tokens: a thread a (kv head, columns) pair
+        const size_t smem_rows = ((talk != nullptr ? (size_t)H * H : 0) +
+                                  (pair_ml != nullptr ? (size_t)H * nvh * splits : 0)) * sizeof(float);
+        if (smem_rows <= 48 * 1024) {
+            const int work = Hkv * dv;
+            const int threads = work >= 256 ? 256 : (work + 31) / 32 * 32;
+            const dim3 grid_rows((work + threads - 1) / threads, T_tokens);
+            if (vec)
+                return slb_launch(mix_heads_gate_rows_kernel<T, 4>, grid_rows, dim3(threads), smem_rows, st, pairs,
+                                  pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
+            return slb_launch(mix_heads_gate_rows_kernel<T, 1>, grid_rows, dim3(threads), smem_rows, st, pairs,
+                              pair_ml, splits, nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
+        }
+    }
+    const int slices = MIX_THREADS / dv < 1 ? 1 : (MIX_THREADS / dv < H ? MIX_THREADS / dv : H);
+    const size_t smem = ((size_t)slices * MIX_HEADS * D + (talk != nullptr ? (size_t)H * H : 0) +
+                         (pair_ml != nullptr ? (size_t)H * splits : 0)) * sizeof(float);
+    constexpr size_t SMEM_MAX = 96 * 1024;
+    if (smem > SMEM_MAX) return SLB_ERR_TOO_LARGE;
+    static unsigned long long configured[2] = {0, 0};  // per template instance, a bit per device
+    const dim3 grid(Hkv, T_tokens);
+    if (vec) {
+        const int rc = slb_configure(&configured[0], mix_heads_gate_kernel<T, 4>, SMEM_MAX);
+        if (rc != 0) return rc;
+        return slb_launch(mix_heads_gate_kernel<T, 4>, grid, dim3(MIX_THREADS), smem, st, pairs, pair_ml, splits,
                           nvh, direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
-    return slb_launch(mix_heads_gate_kernel<T, 1>, grid, dim3(threads), smem, st, pairs, pair_ml, splits, nvh,
+    }
+    const int rc = slb_configure(&configured[1], mix_heads_gate_kernel<T, 1>, SMEM_MAX);
+    if (rc != 0) return rc;
+    return slb_launch(mix_heads_gate_kernel<T, 1>, grid, dim3(MIX_THREADS), smem, st, pairs, pair_ml, splits, nvh,
                       direct, ldi, talk, gate, ldg, out, ldo, H, Hkv, D);
 }
 

@@ -246,8 +246,10 @@ struct TalkArgs {
 // softmax_tile for scores with the distance bias (always masked: the bias needs every
 // distance anyway).  (r1, r2) per row half; r1 is applied in the base-2 domain, where
 // r1 ln(x) log2(e) = r1 log2(x).
+// The accumulators are not touched here: the caller multiplies them by alpha (it may hold
+// several, one per value head).
 template <int NT>
-__device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&o)[NT_O][4], float (&m)[2],
+__device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&alpha)[2], float (&m)[2],
                                                   float (&l)[2], int kpos0, int kend, int pos_lo,
                                                   int pos_hi, int window, float scale_log2,
                                                   const float (&r1)[2], const float (&r2)[2]) {
@@ -265,7 +267,6 @@ __device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&o)[
             mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
         }
     }
-    float alpha[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
@@ -283,16 +284,209 @@ __device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&o)[
         }
         l[h] = l[h] * alpha[h] + sum;
     }
-    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+}
+
+__device__ __forceinline__ void rescale_rows(float (&o)[NT_O][4], const float (&alpha)[2]) {
 #pragma unroll
-        for (int n = 0; n < NT_O; ++n) {
-            o[n][0] *= alpha[0];
-            o[n][1] *= alpha[0];
-            o[n][2] *= alpha[1];
-            o[n][3] *= alpha[1];
+    for (int n = 0; n < NT_O; ++n) {
+        o[n][0] *= alpha[0];
+        o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1];
+        o[n][3] *= alpha[1];
+    }
+}
+
+// S for a 16-row Q tile whose A fragments are fetched from shared memory k-step by k-step
+// (kernels that need their registers for several accumulators).
+template <int NT>
+__device__ __forceinline__ void qk_tile_q_in_smem(float (&s)[NT][4], const bf16* Qs, const bf16* Ks, int krow) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        unsigned a[4];
+        ldmatrix_x4(a, Qs + (lane & 15) * LDS + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int jp = 0; jp < NT / 2; ++jp) {
+            unsigned b[4];
+            ldmatrix_x4(b, Ks + (krow + jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDS + kk * 16 +
+                               ((lane >> 3) & 1) * 8);
+            mma_bf16(s[2 * jp], a, b[0], b[1]);
+            mma_bf16(s[2 * jp + 1], a, b[2], b[3]);
         }
     }
 }
+
+// One TBN-key tile of K (head kvh) and of the values of `nv` heads from vh0 on, V tile j at
+// Vs + j * TBN * LDS.
+template <int TBN>
+__device__ __forceinline__ void load_k_and_value_tiles(bf16* Ks, bf16* Vs, int nv, const bf16* __restrict__ kc,
+                                                       const bf16* __restrict__ vc,
+                                                       const int* __restrict__ table, int k0, int kend,
+                                                       int kvh, int vh0, int Hkv, int ps, int num_pages) {
+    const bool pow2 = (ps & (ps - 1)) == 0;
+    const int shift = __ffs(ps) - 1;
+    for (int idx = threadIdx.x; idx < TBN * CHUNKS; idx += NTHREADS) {
+        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+        const int kp = k0 + r;
+        bool ok = kp < kend;
+        const int lp = pow2 ? kp >> shift : kp / ps;
+        const int slot = pow2 ? kp & (ps - 1) : kp - lp * ps;
+        int page = -1;
+        if (ok) page = table[lp];
+        if (page >= num_pages) {
+            atomicCAS(&attn_status_word, 0, 0x40);
+            page = -1;
+        }
+        ok = ok && page >= 0;
+        const size_t base = ok ? ((size_t)page * Hkv * ps + slot) * D + c * 8 : 0;
+        const size_t head = (size_t)ps * D;
+        cp_async16(Ks + r * LDS + c * 8, kc + base + (ok ? kvh * head : 0), ok);
+        for (int j = 0; j < nv; ++j)
+            cp_async16(Vs + (size_t)j * TBN * LDS + r * LDS + c * 8, vc + base + (ok ? (vh0 + j) * head : 0), ok);
+    }
+}
+
+// Value heads a block of the prefill kernel for mixed heads finishes at once: their float32
+// accumulators (16 rows x D a warp each) must fit in registers beside the scores.
+constexpr int TALK_NV = D <= 64 ? 4 : (D <= 128 ? 2 : 1);
+// Keys a tile: 32 for the large head sizes, so that two blocks (their registers allow no more)
+// also fit an SM's shared memory.
+constexpr int TALK_BN = D <= 64 ? 64 : 32;
+constexpr int TALK_STAGE_ELEMS = (1 + TALK_NV) * TALK_BN * LDS;
+
+// The prefill kernel for mixers with a distance bias and mixed heads: like
+// prefill_attention_kernel, but a block applies its rows' softmax weights to the values of up
+// to TALK_NV kv heads (grid y: groups of TALK_NV value heads), so that scores, bias and
+// exponentials are computed once for them, and writes float32 results per (query head, value
+// head) pair.  grid (tiles x Hkv, ceil(nvh / TALK_NV)).
+__global__ void __launch_bounds__(NTHREADS) talk_prefill_attention_kernel(
+    const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_q,
+    const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
+    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, TalkArgs ta) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
+    bf16* stage0 = Qs + BM * LDS;                          // 2 x (K tile | TALK_NV V tiles)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x % Hkv;
+    const int vh0 = ta.nvh > 1 ? (int)blockIdx.y * TALK_NV : kvh;
+    const int nv = ta.nvh > 1 ? min(TALK_NV, ta.nvh - vh0) : 1;
+    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
+    const int s = tile_seq[tile];
+    const int row0 = tile_row0[tile];
+    const int g = H / Hkv;
+    const int q0 = cu_q[s];
+    const int qlen = cu_q[s + 1] - q0;
+    const int ctx = ctx_len[s];
+    const int nrows = min(BM, qlen * g - row0);
+    if (nrows <= 0) return;
+    const int pos_base = ctx - qlen;
+    const int* table = block_table + (size_t)s * max_pages;
+
+    for (int idx = tid; idx < BM * CHUNKS; idx += NTHREADS) {
+        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+        const bool ok = r < nrows;
+        const int rho = row0 + (ok ? r : 0);
+        const int tl = rho / g, hg = rho - tl * g;
+        cp_async16(Qs + r * LDS + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)(kvh * g + hg) * D + c * 8, ok);
+    }
+    cp_async_commit();
+
+    const int p_first = pos_base + row0 / g;
+    const int p_last = pos_base + (row0 + nrows - 1) / g;
+    int kbeg = 0;
+    if (window > 0) kbeg = max(0, p_first - window + 1) / TALK_BN * TALK_BN;
+    const int kend = p_last + 1;
+    const int ntiles = (kend - kbeg + TALK_BN - 1) / TALK_BN;
+
+    load_k_and_value_tiles<TALK_BN>(stage0, stage0 + TALK_BN * LDS, nv, kc, vc, table, kbeg, kend, kvh, vh0, Hkv, ps, num_pages);
+    cp_async_commit();
+
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
+    const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
+    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
+    if (ta.r1 != nullptr) {
+        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + (row0 + r_lo) % g]; br2[0] = ta.r2[kvh * g + (row0 + r_lo) % g]; }
+        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + (row0 + r_hi) % g]; br2[1] = ta.r2[kvh * g + (row0 + r_hi) % g]; }
+    }
+    const int wr_last = min(nrows - 1, warp * 16 + 15);
+    const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
+
+    float o[TALK_NV][NT_O][4];
+#pragma unroll
+    for (int j = 0; j < TALK_NV; ++j)
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[j][n][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int t = 0; t < ntiles; ++t) {
+        bf16* Ks = stage0 + (t & 1) * TALK_STAGE_ELEMS;
+        bf16* Vs = Ks + TALK_BN * LDS;
+        if (t + 1 < ntiles) {
+            bf16* Kn = stage0 + ((t + 1) & 1) * TALK_STAGE_ELEMS;
+            load_k_and_value_tiles<TALK_BN>(Kn, Kn + TALK_BN * LDS, nv, kc, vc, table, kbeg + (t + 1) * TALK_BN, kend, kvh, vh0, Hkv,
+                                   ps, num_pages);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int k0 = kbeg + t * TALK_BN;
+        if (k0 <= warp_pos_max) {                          // else: every key is in this warp's future
+            float sc[TALK_BN / 8][4];
+            qk_tile_q_in_smem<TALK_BN / 8>(sc, Qs + warp * 16 * LDS, Ks, 0);
+            float alpha[2];
+            softmax_tile_bias<TALK_BN / 8>(sc, alpha, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+#pragma unroll
+            for (int j = 0; j < TALK_NV; ++j) {
+                if (j < nv) {
+                    if (rescale) rescale_rows(o[j], alpha);
+                    pv_tile<TALK_BN / 8>(o[j], sc, Vs + (size_t)j * TALK_BN * LDS, 0);
+                }
+            }
+        }
+        __syncthreads();                                   // the stage may be refilled next round
+    }
+
+    pdl_launch_dependents();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f;
+    const float inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TALK_NV; ++j) {
+        if (j >= nv) break;
+        const int vhi = ta.nvh > 1 ? vh0 + j : 0;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = half ? r_hi : r_lo;
+            if (row >= nrows) continue;
+            const int rho = row0 + row;
+            const int tl = rho / g, hg = rho - tl * g;
+            const float inv = half ? inv_hi : inv_lo;
+            float* dst = ta.pair_o + (((size_t)(q0 + tl) * H + (size_t)(kvh * g + hg)) * ta.nvh + vhi) * D +
+                         (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[j][n][2 * half] * inv, o[j][n][2 * half + 1] * inv);
+        }
+    }
+}
+
 
 // ------------------------------------------------------------------- prefill
 // TALK: grid (tiles x Hkv, nvh); blockIdx.y names the value head when nvh > 1.
@@ -388,9 +582,11 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
             // all 64 keys visible to all 16 rows of the warp: no mask to evaluate
             const bool open = warp_rows_full && k0 + BN - 1 <= warp_pos_min &&
                               (window <= 0 || warp_pos_max - k0 < window);
-            if (TALK)
-                softmax_tile_bias<BN / 8>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
-            else if (open)
+            if (TALK) {
+                float alpha[2];
+                softmax_tile_bias<BN / 8>(sc, alpha, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) rescale_rows(o, alpha);
+            } else if (open)
                 softmax_tile<BN / 8, false>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<BN / 8, true>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
@@ -550,9 +746,11 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
             // every key of this warp's 16 is inside the context and the window: no mask
-            if (TALK)
-                softmax_tile_bias<2>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
-            else if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
+            if (TALK) {
+                float alpha[2];
+                softmax_tile_bias<2>(sc, alpha, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) rescale_rows(o, alpha);
+            } else if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
                 softmax_tile<2, false>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
@@ -724,12 +922,13 @@ int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, cons
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16 || (uintptr_t)pair_o % 8) return SLB_ERR_BAD_ARG;
     if ((long long)num_tiles * Hkv > 0x7fffffffll || Hkv > 65535) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;
-    const int crc = slb_configure(&configured, prefill_attention_kernel<true>, PREFILL_SMEM);
+    constexpr size_t SMEM = (size_t)(BM * LDS + 2 * TALK_STAGE_ELEMS) * sizeof(bf16);
+    const int crc = slb_configure(&configured, talk_prefill_attention_kernel, SMEM);
     if (crc != 0) return crc;
     const int nvh = every_pair ? Hkv : 1;
-    return slb_launch(prefill_attention_kernel<true>, dim3((unsigned)num_tiles * Hkv, nvh), dim3(NTHREADS),
-                      PREFILL_SMEM, st, q, ldq, kc, vc, (bf16*)nullptr, 0, block_table, max_pages, cu_q, ctx_len,
-                      tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
+    return slb_launch(talk_prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv, (nvh + TALK_NV - 1) / TALK_NV),
+                      dim3(NTHREADS), SMEM, st, q, ldq, kc, vc, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
                       TalkArgs{r1, r2, pair_o, nullptr, nvh});
 }
 
