@@ -19,13 +19,13 @@
 // Masking: key r is visible to a query at position a iff r <= a and, with a
 // window w > 0, a - r < w.  Page layout: [page][kv head][slot][SLB_HEAD_DIM].
 //
-// Both kernels also exist in a second instance (TALK) for mixers that change scores and
-// weights: a log-distance bias r1_h ln(1 + r2_h (a - r)) is subtracted from the scaled score,
-// the values may come from another kv head than the keys (the grid names it), and the
-// result leaves in float32 per (query head, value head) pair -- normalised from the prefill
-// kernel, as unnormalised split partials with their (max, sum) from the decode kernel -- for
-// the kernel that mixes heads after the softmax (slb_mix_heads_gate in the core library),
-// which also combines the decode kernel's splits.
+// For mixers that change scores and weights there is a prefill kernel of its own
+// (talk_prefill_attention_kernel) and a second instance of the decode kernel (TALK): a
+// log-distance bias r1_h ln(1 + r2_h (a - r)) is subtracted from the scaled score, the values
+// may come from other kv heads than the keys, and the result leaves in float32 per (query head,
+// value head) pair -- normalised from the prefill kernel, as unnormalised split partials with
+// their (max, sum) from the decode kernel -- for the kernel that mixes heads after the softmax
+// (slb_mix_heads_gate in the core library), which also combines the decode kernel's splits.
 //
 // Reference analogue: the one-program-per-(sequence, head) Triton decode kernel
 // (servelab/attention/triton/paged_attention.py:25-74), which has no tensor-core
@@ -489,14 +489,12 @@ __global__ void __launch_bounds__(NTHREADS) talk_prefill_attention_kernel(
 
 
 // ------------------------------------------------------------------- prefill
-// TALK: grid (tiles x Hkv, nvh); blockIdx.y names the value head when nvh > 1.
-template <bool TALK>
 __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
     const int* __restrict__ tile_seq, const int* __restrict__ tile_row0, int H, int Hkv, int ps,
-    int num_pages, float scale_log2, int window, TalkArgs ta) {
+    int num_pages, float scale_log2, int window) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS], later the output stage
@@ -507,7 +505,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     // started first, all kv heads of a tile together (blocks start in the order of their
     // linear index)
     const int kvh = blockIdx.x % Hkv;
-    const int vh = (TALK && ta.nvh > 1) ? (int)blockIdx.y : kvh;
+    const int vh = kvh;
     const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);
     const int s = tile_seq[tile];
     const int row0 = tile_row0[tile];
@@ -544,11 +542,6 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
-    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
-    if (TALK && ta.r1 != nullptr) {
-        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + (row0 + r_lo) % g]; br2[0] = ta.r2[kvh * g + (row0 + r_lo) % g]; }
-        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + (row0 + r_hi) % g]; br2[1] = ta.r2[kvh * g + (row0 + r_hi) % g]; }
-    }
     const int wr_last = min(nrows - 1, warp * 16 + 15);
     const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
     const bool warp_rows_full = warp * 16 + 15 < nrows;
@@ -582,11 +575,7 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
             // all 64 keys visible to all 16 rows of the warp: no mask to evaluate
             const bool open = warp_rows_full && k0 + BN - 1 <= warp_pos_min &&
                               (window <= 0 || warp_pos_max - k0 < window);
-            if (TALK) {
-                float alpha[2];
-                softmax_tile_bias<BN / 8>(sc, alpha, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
-                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) rescale_rows(o, alpha);
-            } else if (open)
+            if (open)
                 softmax_tile<BN / 8, false>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<BN / 8, true>(sc, o, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2);
@@ -604,24 +593,6 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
     }
     const float inv_lo = l[0] > 0.f ? 1.f / l[0] : 0.f;
     const float inv_hi = l[1] > 0.f ? 1.f / l[1] : 0.f;
-    if (TALK) {
-        // float32 results of this (query head, value head) pair, straight from the registers
-        const int vhi = ta.nvh > 1 ? vh : 0;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int row = half ? r_hi : r_lo;
-            if (row >= nrows) continue;
-            const int rho = row0 + row;
-            const int tl = rho / g, hg = rho - tl * g;
-            const float inv = half ? inv_hi : inv_lo;
-            float* dst = ta.pair_o + (((size_t)(q0 + tl) * H + (size_t)(kvh * g + hg)) * ta.nvh + vhi) * D +
-                         (lane & 3) * 2;
-#pragma unroll
-            for (int n = 0; n < NT_O; ++n)
-                *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
-        }
-        return;
-    }
     bf16* Os = Qs + warp * 16 * LDS;
     __syncwarp();
 #pragma unroll
@@ -900,14 +871,14 @@ int slb_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf1
         return SLB_ERR_BAD_ARG;                            // 16-byte copies
     if ((long long)num_tiles * Hkv > 0x7fffffffll) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;              // a bit per device
-    const int crc = slb_configure(&configured, prefill_attention_kernel<false>, PREFILL_SMEM);
+    const int crc = slb_configure(&configured, prefill_attention_kernel, PREFILL_SMEM);
     if (crc != 0) return crc;
-    return slb_launch(prefill_attention_kernel<false>, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
+    return slb_launch(prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv), dim3(NTHREADS), PREFILL_SMEM, st,
                       q, ldq, kc, vc, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window, TalkArgs{});
+                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window);
 }
 
-// The TALK instance of the prefill kernel: pair_o float32 [T][H][nvh][D], nvh = Hkv when
+// The prefill kernel for mixed heads: pair_o float32 [T][H][nvh][D], nvh = Hkv when
 // every_pair (each query head's weights applied to every kv head's values), else 1.
 int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
                                     const int* block_table, int max_pages, const int* cu_q,
@@ -916,7 +887,7 @@ int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, cons
                                     int window, const float* r1, const float* r2, float* pair_o,
                                     int every_pair, cudaStream_t st) {
     if (num_tiles <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) ||
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale == scale) ||
         pair_o == nullptr || (r1 == nullptr) != (r2 == nullptr))
         return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16 || (uintptr_t)pair_o % 8) return SLB_ERR_BAD_ARG;
@@ -940,7 +911,7 @@ int slb_talk_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const
                                    int num_splits, const float* r1, const float* r2, float* pair_o,
                                    float* pair_ml, int every_pair, cudaStream_t st) {
     if (S <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale > 0.f) ||
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || !(scale == scale) ||
         pair_o == nullptr || pair_ml == nullptr || (r1 == nullptr) != (r2 == nullptr) || num_splits < 1)
         return SLB_ERR_BAD_ARG;
     if (ldq % 8 || ((uintptr_t)q | (uintptr_t)kc | (uintptr_t)vc) % 16) return SLB_ERR_BAD_ARG;

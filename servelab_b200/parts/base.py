@@ -22,7 +22,7 @@ Kinds of part and what each must provide (beyond ``declare`` and ``load``):
                      with ``out_rows`` (int32 row indices) only those rows are
                      produced and ``resid`` is left as it is.
   Mixer              ``cache_request(spec)`` (class method) -> PagedKVRequest,
-                     FixedStateRequest or None; ``forward(ctx, x, cache,
+                     FixedStateRequest, a tuple of both, or None; ``forward(ctx, x, cache,
                      owns_cache)`` -> [T, hidden] in the compute dtype.  ``cache``
                      is the ``LayerCache`` of the layer whose cache this run uses;
                      with ``owns_cache`` False the mixer must not write it.
@@ -61,9 +61,10 @@ class BuildEnv:
 class LayerCache:
     """Device memory of one layer's cache, handed to its mixer each step.
 
-    Paged: ``k`` and ``v`` are [num_pages, kv_heads, page_size, head_dim] and
-    ``group`` indexes ``ctx.block_tables``.  Fixed state: ``state`` is
-    [num_slots, *shape] float32, indexed by ``ctx.state_slots``.
+    Paged: ``k`` and ``v`` are [num_pages, kv_heads, page_size, head_dim] (one and the same
+    tensor for a request with tied values) and ``group`` indexes ``ctx.block_tables``.  Fixed
+    state: ``state`` is [num_slots, *shape] float32, indexed by ``ctx.state_slots``.  A mixer
+    that asked for both gets both.
     """
     group: int = -1
     k: Optional[torch.Tensor] = None
