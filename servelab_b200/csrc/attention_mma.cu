@@ -19,8 +19,8 @@
 // Masking: key r is visible to a query at position a iff r <= a and, with a
 // window w > 0, a - r < w.  Page layout: [page][kv head][slot][SLB_HEAD_DIM].
 //
-// For mixers that change scores and weights there is a prefill kernel of its own
-// (talk_prefill_attention_kernel) and a second instance of the decode kernel (TALK): a
+// For mixers that change scores and weights there is a prefill and a decode kernel of their own
+// (talk_prefill_attention_kernel, talk_decode_attention_kernel): a
 // log-distance bias r1_h ln(1 + r2_h (a - r)) is subtracted from the scaled score, the values
 // may come from other kv heads than the keys, and the result leaves in float32 per (query head,
 // value head) pair -- normalised from the prefill kernel, as unnormalised split partials with
@@ -234,7 +234,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NT_O]
     }
 }
 
-// What the TALK instances add to a launch.
+// What the kernels for mixed heads take besides the plain kernels' arguments.
 struct TalkArgs {
     const float* r1;       // [H] distance bias: r1_h ln(1 + r2_h distance) leaves the scaled score
     const float* r2;       // [H]
@@ -618,15 +618,11 @@ __global__ void __launch_bounds__(NTHREADS) prefill_attention_kernel(
 // grid (num_splits, Hkv * head_tiles, S); q_len must be 1 for every request.
 // Scratch: part_o [S][H][num_splits][D] float32 (unnormalised), part_ml
 // [S][H][num_splits][2] float32 (running max in the base-2 domain, running sum).
-// TALK: grid (num_splits * nvh, Hkv * head_tiles, S); results always leave as partials in
-// ta.pair_o / ta.pair_ml (the kernel that mixes the heads combines the splits).
-template <bool TALK>
 __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ ctx_len, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles,
-    TalkArgs ta) {
+    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
@@ -636,10 +632,9 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     __shared__ __align__(8) uint64_t full_bar[DSTAGES];    // a stage's K and V rows have landed
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = TALK ? blockIdx.x % num_splits : blockIdx.x;
+    const int split = blockIdx.x;
     const int kvh = blockIdx.y / head_tiles, htile = blockIdx.y - kvh * head_tiles;
-    const int vh = (TALK && ta.nvh > 1) ? (int)(blockIdx.x / num_splits) : kvh;
-    const int vhi = (TALK && ta.nvh > 1) ? vh : 0;
+    const int vh = kvh;
     const int s = blockIdx.z;
     const int g = H / Hkv;
     const int h0 = htile * 16;                             // first head of the group in this tile
@@ -684,11 +679,6 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     const int pos_lo = r_lo < nrows ? pos : -1;
     const int pos_hi = r_hi < nrows ? pos : -1;
-    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
-    if (TALK && ta.r1 != nullptr) {
-        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + h0 + r_lo]; br2[0] = ta.r2[kvh * g + h0 + r_lo]; }
-        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + h0 + r_hi]; br2[1] = ta.r2[kvh * g + h0 + r_hi]; }
-    }
     unsigned qf[KSTEPS][4];
     float o[NT_O][4];
 #pragma unroll
@@ -717,11 +707,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
             // every key of this warp's 16 is inside the context and the window: no mask
-            if (TALK) {
-                float alpha[2];
-                softmax_tile_bias<2>(sc, alpha, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
-                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) rescale_rows(o, alpha);
-            } else if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
+            if (k0 + 15 < ctx && (window <= 0 || pos - k0 < window))
                 softmax_tile<2, false>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
             else
                 softmax_tile<2, true>(sc, o, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2);
@@ -736,13 +722,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
                 mbar_wait(&full_bar[tt % DSTAGES], (tt / DSTAGES) & 1);
             // the combine step must not merge what an earlier launch left in these slots:
             // mark this split of every head as empty (maximum -inf, sum 0)
-            if (TALK) {
-                if (tid < nrows) {
-                    const size_t pi = (((size_t)s * H + kvh * g + h0 + tid) * ta.nvh + vhi) * num_splits + split;
-                    ta.pair_ml[pi * 2] = -INFINITY;
-                    ta.pair_ml[pi * 2 + 1] = 0.f;
-                }
-            } else if (num_splits > 1 && tid < nrows) {
+            if (num_splits > 1 && tid < nrows) {
                 const size_t pi = ((size_t)s * H + kvh * g + h0 + tid) * num_splits + split;
                 part_ml[pi * 2] = -INFINITY;
                 part_ml[pi * 2 + 1] = 0.f;
@@ -787,11 +767,7 @@ __global__ void __launch_bounds__(NTHREADS) decode_attention_kernel(
             }
         }
         const int head = kvh * g + h0 + r;
-        if (TALK) {
-            const size_t pi = (((size_t)s * H + head) * ta.nvh + vhi) * num_splits + split;
-            ta.pair_o[pi * D + d] = acc;
-            if (d == 0) { ta.pair_ml[pi * 2] = M; ta.pair_ml[pi * 2 + 1] = L; }
-        } else if (num_splits == 1) {
+        if (num_splits == 1) {
             out[(size_t)s * ldo + (size_t)head * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
             const size_t pi = ((size_t)s * H + head) * num_splits + split;
@@ -831,6 +807,173 @@ constexpr size_t DECODE_RED_BYTES = (size_t)4 * 16 * D * sizeof(float);
 constexpr size_t DECODE_SMEM = (size_t)16 * LDS * sizeof(bf16) +
                                (DECODE_STAGE_BYTES > DECODE_RED_BYTES ? DECODE_STAGE_BYTES : DECODE_RED_BYTES);
 
+
+// ---------------------------------------------------- decode, mixed heads
+// Value heads a block of the decode kernel for mixed heads finishes at once, and the depth of
+// its ring (each stage holds a K tile and TALK_NV value tiles).
+constexpr int TALK_DSTAGES = 2;
+constexpr int TALK_DSTAGE_ELEMS = (1 + TALK_NV) * BN * LDS;
+
+// grid (num_splits * groups, Hkv * head_tiles, S), groups = ceil(nvh / TALK_NV); q_len 1.
+// Like decode_attention_kernel, with the distance bias, and the softmax weights of the block's
+// query heads applied to the values of up to TALK_NV kv heads, so that scores, bias and
+// exponentials are computed once for them and a key tile is fetched once per group.  Tiles
+// arrive by 16-byte cp.async through a ring of TALK_DSTAGES stages (a bulk copy per 128- or
+// 256-byte row, as in the kernel above, is bounded by the rate of the copies, not by their
+// bytes, once a stage holds five tiles).  Results always leave as split partials:
+// ta.pair_o [S][H][nvh][splits][D], ta.pair_ml [...][2].
+__global__ void __launch_bounds__(NTHREADS) talk_decode_attention_kernel(
+    const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ ctx_len, int H, int Hkv,
+    int ps, int num_pages, float scale_log2, int window, int num_splits, int head_tiles, TalkArgs ta) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][LDS]
+    bf16* stage0 = Qs + 16 * LDS;
+    float* red_o = reinterpret_cast<float*>(stage0);       // [4][16][D] after the key loop
+    __shared__ float red_m[4][16], red_l[4][16];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x % num_splits;
+    const int kvh = blockIdx.y / head_tiles, htile = blockIdx.y - kvh * head_tiles;
+    const int vh0 = ta.nvh > 1 ? (int)(blockIdx.x / num_splits) * TALK_NV : kvh;
+    const int nv = ta.nvh > 1 ? min(TALK_NV, ta.nvh - vh0) : 1;
+    const int s = blockIdx.z;
+    const int g = H / Hkv;
+    const int h0 = htile * 16;
+    const int nrows = min(16, g - h0);
+    const int ctx = ctx_len[s];
+    const int pos = ctx - 1;
+    const int* table = block_table + (size_t)s * max_pages;
+
+    int kbeg = 0;
+    if (window > 0) kbeg = max(0, pos - window + 1) / BN * BN;
+    const int total_tiles = (ctx - kbeg + BN - 1) / BN;
+    const int tiles_per_split = (total_tiles + num_splits - 1) / num_splits;
+    const int t_begin = split * tiles_per_split;
+    const int t_end = min(total_tiles, t_begin + tiles_per_split);
+    const int ntiles = max(0, t_end - t_begin);
+    const int kstart = kbeg + t_begin * BN;
+
+    for (int idx = tid; idx < 16 * CHUNKS; idx += NTHREADS) {
+        const int r = idx / CHUNKS, c = idx - r * CHUNKS;
+        const bool ok = r < nrows;
+        cp_async16(Qs + r * LDS + c * 8,
+                   q + (size_t)s * ldq + (size_t)(kvh * g + h0 + (ok ? r : 0)) * D + c * 8, ok);
+    }
+    cp_async_commit();
+    // TALK_DSTAGES - 1 tiles are in flight ahead of the one being used; a group is committed every
+    // round, loads or not, so that "all but the newest TALK_DSTAGES - 1 groups" names tile t
+#pragma unroll
+    for (int p = 0; p < TALK_DSTAGES - 1; ++p) {
+        if (p < ntiles) {
+            bf16* Kp = stage0 + p * TALK_DSTAGE_ELEMS;
+            load_k_and_value_tiles<BN>(Kp, Kp + BN * LDS, nv, kc, vc, table, kstart + p * BN, ctx, kvh, vh0, Hkv,
+                                       ps, num_pages);
+        }
+        cp_async_commit();
+    }
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const int pos_lo = r_lo < nrows ? pos : -1;
+    const int pos_hi = r_hi < nrows ? pos : -1;
+    float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
+    if (ta.r1 != nullptr) {
+        if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + h0 + r_lo]; br2[0] = ta.r2[kvh * g + h0 + r_lo]; }
+        if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + h0 + r_hi]; br2[1] = ta.r2[kvh * g + h0 + r_hi]; }
+    }
+    unsigned qf[KSTEPS][4];
+    float o[TALK_NV][NT_O][4];
+#pragma unroll
+    for (int j = 0; j < TALK_NV; ++j)
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[j][n][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int t = 0; t < ntiles; ++t) {
+        bf16* Ks = stage0 + (t % TALK_DSTAGES) * TALK_DSTAGE_ELEMS;
+        const int tn = t + TALK_DSTAGES - 1;                 // its stage was freed by round t - 1
+        if (tn < ntiles) {
+            bf16* Kn = stage0 + (tn % TALK_DSTAGES) * TALK_DSTAGE_ELEMS;
+            load_k_and_value_tiles<BN>(Kn, Kn + BN * LDS, nv, kc, vc, table, kstart + tn * BN, ctx, kvh, vh0, Hkv,
+                                       ps, num_pages);
+        }
+        cp_async_commit();
+        cp_async_wait<TALK_DSTAGES - 1>();
+        __syncthreads();                                     // tile t (and, at first, the Q rows) of all threads
+        if (t == 0) load_q_frags(qf, Qs);
+        const int k0 = kstart + t * BN + warp * 16;         // this warp's 16 keys of the tile
+        if (k0 < ctx) {
+            float sc[2][4];
+            qk_tile<2>(sc, qf, Ks, warp * 16);
+            float alpha[2];
+            softmax_tile_bias<2>(sc, alpha, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+#pragma unroll
+            for (int j = 0; j < TALK_NV; ++j) {
+                if (j < nv) {
+                    if (rescale) rescale_rows(o[j], alpha);
+                    pv_tile<2>(o[j], sc, Ks + (size_t)(1 + j) * BN * LDS, warp * 16);
+                }
+            }
+        }
+        __syncthreads();                                     // the stage may be refilled next round
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    pdl_launch_dependents();
+    // merge the four warps (each saw a quarter of the keys), one value head after the other
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    if ((lane & 3) == 0) {
+        red_m[warp][r_lo] = m[0]; red_l[warp][r_lo] = l[0];
+        red_m[warp][r_hi] = m[1]; red_l[warp][r_hi] = l[1];
+    }
+#pragma unroll
+    for (int j = 0; j < TALK_NV; ++j) {
+        if (j >= nv) break;                                  // (uniform over the block)
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n) {
+            const int col = n * 8 + (lane & 3) * 2;
+            float* dst = red_o + ((size_t)warp * 16 + r_lo) * D + col;
+            dst[0] = o[j][n][0]; dst[1] = o[j][n][1];
+            dst[8 * D] = o[j][n][2]; dst[8 * D + 1] = o[j][n][3];
+        }
+        __syncthreads();
+        const int vhi = ta.nvh > 1 ? vh0 + j : 0;
+        for (int idx = tid; idx < nrows * D; idx += NTHREADS) {
+            const int r = idx / D, d = idx - r * D;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, red_m[w][r]);
+            float L = 0.f, acc = 0.f;
+            if (M != -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    if (red_m[w][r] == -INFINITY) continue;
+                    const float f = exp2f(red_m[w][r] - M);
+                    L += red_l[w][r] * f;
+                    acc += red_o[((size_t)w * 16 + r) * D + d] * f;
+                }
+            }
+            const size_t pi = (((size_t)s * H + kvh * g + h0 + r) * ta.nvh + vhi) * num_splits + split;
+            ta.pair_o[pi * D + d] = acc;
+            if (d == 0) { ta.pair_ml[pi * 2] = M; ta.pair_ml[pi * 2 + 1] = L; }
+        }
+        __syncthreads();                                     // red_o is rewritten for the next value head
+    }
+}
+
+constexpr size_t TALK_DECODE_STAGE_BYTES = (size_t)TALK_DSTAGES * TALK_DSTAGE_ELEMS * sizeof(bf16);
+constexpr size_t TALK_DECODE_SMEM = (size_t)16 * LDS * sizeof(bf16) +
+                                    (TALK_DECODE_STAGE_BYTES > DECODE_RED_BYTES ? TALK_DECODE_STAGE_BYTES : DECODE_RED_BYTES);
+
 }  // namespace
 
 SLB_DEFINE_PDL_SWITCH
@@ -851,6 +994,7 @@ int slb_attention_status(int reset) {
     return v;
 }
 int slb_prefill_attention_tile_rows() { return BM; }
+int slb_talk_attention_value_heads() { return TALK_NV; }
 int slb_decode_attention_max_splits() { return MAX_SPLITS; }
 
 // bytes of scratch the decode kernel needs for (S requests, H heads, num_splits)
@@ -903,7 +1047,7 @@ int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, cons
                       TalkArgs{r1, r2, pair_o, nullptr, nvh});
 }
 
-// The TALK instance of the decode kernel: partials pair_o float32 [S][H][nvh][splits][D] and
+// The decode kernel for mixed heads: partials pair_o float32 [S][H][nvh][splits][D] and
 // pair_ml [S][H][nvh][splits][2]; nothing is combined here.
 int slb_talk_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc,
                                    const int* block_table, int max_pages, const int* ctx_len, int S,
@@ -920,12 +1064,13 @@ int slb_talk_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const
     const int head_tiles = (g + 15) / 16;
     if (num_splits > MAX_SPLITS || S > 65535 || Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;
-    const int crc = slb_configure(&configured, decode_attention_kernel<true>, DECODE_SMEM);
+    const int crc = slb_configure(&configured, talk_decode_attention_kernel, TALK_DECODE_SMEM);
     if (crc != 0) return crc;
-    return slb_launch(decode_attention_kernel<true>, dim3(num_splits * nvh, Hkv * head_tiles, S), dim3(NTHREADS),
-                      DECODE_SMEM, st, q, ldq, kc, vc, (bf16*)nullptr, 0, block_table, max_pages, ctx_len,
-                      (float*)nullptr, (float*)nullptr, H, Hkv, ps, num_pages, scale * 1.4426950408889634f,
-                      window, num_splits, head_tiles, TalkArgs{r1, r2, pair_o, pair_ml, nvh});
+    const int groups = (nvh + TALK_NV - 1) / TALK_NV;
+    return slb_launch(talk_decode_attention_kernel, dim3(num_splits * groups, Hkv * head_tiles, S), dim3(NTHREADS),
+                      TALK_DECODE_SMEM, st, q, ldq, kc, vc, block_table, max_pages, ctx_len, H, Hkv, ps, num_pages,
+                      scale * 1.4426950408889634f, window, num_splits, head_tiles,
+                      TalkArgs{r1, r2, pair_o, pair_ml, nvh});
 }
 
 // scratch: float32 buffer of at least slb_decode_attention_scratch_bytes(...) bytes
@@ -944,14 +1089,14 @@ int slb_decode_attention_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
     const int head_tiles = (g + 15) / 16;
     if (Hkv * head_tiles > 65535) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;              // a bit per device
-    const int crc = slb_configure(&configured, decode_attention_kernel<false>, DECODE_SMEM);
+    const int crc = slb_configure(&configured, decode_attention_kernel, DECODE_SMEM);
     if (crc != 0) return crc;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * H * num_splits * D : nullptr;
-    const int rc = slb_launch(decode_attention_kernel<false>, dim3(num_splits, Hkv * head_tiles, S),
+    const int rc = slb_launch(decode_attention_kernel, dim3(num_splits, Hkv * head_tiles, S),
                               dim3(NTHREADS), DECODE_SMEM, st, q, ldq, kc, vc, out, ldo, block_table,
                               max_pages, ctx_len, part_o, part_ml, H, Hkv, ps, num_pages,
-                              scale * 1.4426950408889634f, window, num_splits, head_tiles, TalkArgs{});
+                              scale * 1.4426950408889634f, window, num_splits, head_tiles);
     if (rc != 0 || num_splits == 1) return rc;
     return slb_launch(decode_combine_kernel, dim3(H, S), dim3((D + 31) / 32 * 32), 0, st,
                       (const float*)part_o, (const float*)part_ml, out, ldo, H, num_splits);

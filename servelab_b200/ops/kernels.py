@@ -281,12 +281,13 @@ def talk_prefill_attention(ctx, q, k_cache, v_cache, block_table, num_heads, num
         _stream()), "talk_prefill_attention")
 
 
-def talk_decode_splits(num_seqs: int, num_kv_heads: int, group: int, nvh: int, longest_context: int,
-                       window: int, max_splits: int) -> int:
+def talk_decode_splits(num_seqs: int, num_kv_heads: int, group: int, value_groups: int,
+                       longest_context: int, window: int, max_splits: int) -> int:
     """Key splits of the decode kernel for mixed heads: enough blocks for ``decode_ctas_per_sm``
-    per SM, at most one split per 64 keys a query can see."""
+    per SM, at most one split per 64 keys a query can see.  ``value_groups``: blocks per (request,
+    kv head), each finishing a group of value heads."""
     seen = min(longest_context, window + 63) if window > 0 else longest_context
-    ctas = num_seqs * num_kv_heads * nvh * ((group + 15) // 16)
+    ctas = num_seqs * num_kv_heads * value_groups * ((group + 15) // 16)
     want = max(1, (decode_ctas_per_sm * _num_sms()) // max(ctas, 1))
     return max(1, min(want, max_splits, -(-seen // 64)))
 
@@ -298,8 +299,9 @@ def talk_decode_attention(ctx, q, k_cache, v_cache, block_table, num_heads, num_
     ``mix_heads_gate`` combines."""
     lib = L.attention(head_dim)
     S = ctx.num_seqs
-    splits = talk_decode_splits(S, num_kv_heads, num_heads // num_kv_heads, nvh, ctx.split_hint_len,
-                                window, lib.slb_decode_attention_max_splits())
+    per_block = lib.slb_talk_attention_value_heads()
+    splits = talk_decode_splits(S, num_kv_heads, num_heads // num_kv_heads, -(-nvh // per_block),
+                                ctx.split_hint_len, window, lib.slb_decode_attention_max_splits())
     pairs = torch.empty((S, num_heads, nvh, splits, head_dim), dtype=_F32, device=q.device)
     pair_ml = torch.empty((S, num_heads, nvh, splits, 2), dtype=_F32, device=q.device)
     L.check(lib.slb_talk_decode_attention_bf16(

@@ -171,6 +171,7 @@ _ATTN_SIGNATURES = {
     "slb_decode_attention_ws_splits_used": [I],
     "slb_decode_attention_ws_max_splits": [],
     "slb_decode_attention_ws_tile_keys": [],
+    "slb_talk_attention_value_heads": [],
     "slb_talk_prefill_attention_bf16": [P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P, P, P, I, P],
     "slb_talk_decode_attention_bf16": [P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P, P, P, P, I, P],
 }
