@@ -24,7 +24,7 @@ P = {"architecture": "Dezelorn", "vocab": 211, "width": 48, "embedding": {"scale
                 _layer(_mixer(4, 4, 16, 1, 1000, 0.5, 3, 0.25), 40)]}
 Q = {"architecture": "Dezelorn", "vocab": 300, "width": 80, "embedding": {"scale": 9.0},
      "norm": {"eps": 1e-5},
-     "layers": [_layer(_mixer(4, 2, 64, 4, 70, 0.3, 32, 0.11), 120),
+     "layers": [_layer(_mixer(6, 2, 64, 3, 70, 0.35, 32, 0.11), 120),
                 _layer(_mixer(3, 1, 24, 2, 1, 0.1, 7, 0.2), 96),
                 _layer(_mixer(8, 2, 32, 6, 17, 0.25, 64, 0.15), None),
                 _layer(_mixer(2, 2, 64, 2, 130, 0.6, 10, 0.12), 64)]}

@@ -195,8 +195,8 @@ def _run_attention(case, H_, Hkv, D, window, ps, talk=True):
 
 
 SHAPES = [  # heads, kv heads, head size, window, page size
-    (4, 2, 64, 40, 16), (6, 3, 16, 12, 8), (2, 1, 32, 33, 4), (4, 4, 16, 1000, 16), (3, 1, 24, 5, 8),
-    (8, 2, 128, 70, 16), (4, 2, 64, 1, 16)]
+    (6, 2, 64, 44, 16), (6, 3, 16, 12, 8), (2, 1, 32, 33, 4), (4, 4, 16, 1000, 16), (3, 1, 24, 5, 8),
+    (8, 2, 128, 70, 16), (6, 3, 64, 1, 16), (12, 4, 128, 50, 8), (5, 5, 48, 9, 16)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
