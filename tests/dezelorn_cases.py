@@ -3,7 +3,7 @@ include the values a model could happen to make equal or 1: one kv head, as many
 heads, one tap (no convolution, no state), a window of one key, a window longer than any
 request, a temperature that changes every few tokens, layers without a feed-forward and
 layers that differ inside one model, head sizes the tensor-core kernels take (16, 32, 64) and
-one they do not (24)."""
+one they do not (24); a third model has sizes that fit no 16-byte access."""
 
 from __future__ import annotations
 
@@ -28,7 +28,12 @@ Q = {"architecture": "Dezelorn", "vocab": 300, "width": 80, "embedding": {"scale
                 _layer(_mixer(3, 1, 24, 2, 1, 0.1, 7, 0.2), 96),
                 _layer(_mixer(8, 2, 32, 6, 17, 0.25, 64, 0.15), None),
                 _layer(_mixer(2, 2, 64, 2, 130, 0.6, 10, 0.12), 64)]}
-CASES = {"P": (P, 5, 8), "Q": (Q, 9, 16)}        # config, seed, page size
+# sizes that no 16-byte access fits: odd width, head sizes 20 and 10, 3 kv heads for 3 heads
+R = {"architecture": "Dezelorn", "vocab": 97, "width": 50, "embedding": {"scale": 4.0},
+     "norm": {"eps": 1e-5},
+     "layers": [_layer(_mixer(3, 3, 20, 2, 25, 0.45, 4, 0.22), 30),
+                _layer(_mixer(2, 1, 10, 3, 9, 0.15, 11, 0.4), 18)]}
+CASES = {"P": (P, 5, 8), "Q": (Q, 9, 16), "R": (R, 13, 4)}        # config, seed, page size
 STD_OF = {"embed": 0.12, "head": 0.1, ".mix.q": 0.25, ".mix.k": 0.25, ".conv": 0.5}
 
 

@@ -257,7 +257,7 @@ LENGTHS = [70, 45, 190, 33, 2, 1, 58]
 TOL = {"float32": 1e-5, "bfloat16": 1.5e-2}       # about twice the worst error the tests print
 
 
-@pytest.fixture(scope="module", params=["P", "Q"])
+@pytest.fixture(scope="module", params=["P", "Q", "R"])
 def model(request, tmp_path_factory):
     cfg, seed, page = C.CASES[request.param]
     folder = C.make_model(str(tmp_path_factory.mktemp(f"dez_{request.param}")), cfg, seed)
@@ -381,6 +381,28 @@ def test_single_token_steps_through_replayed_graphs(model, dtype):
         for pos in eager[rid]:
             assert np.abs(graphs[rid][pos] - eager[rid][pos]).max() <= (2e-6 if dtype == "float32" else 1e-1)
     _compare(model, dtype, graphs)
+
+
+def test_the_trace_runner_as_a_program(model, tmp_path):
+    """bin/trace_run on a model folder, steps on standard input, logits in files: the mixed
+    trace in bfloat16, rows against the oracle."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = H.trace_mixed(model["requests"], seed=21)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model["folder"], "--dtype", "bfloat16",
+         "--out", str(out), "--max-tokens", str(H.peak_tokens(steps)), "--page-size", str(model["page"])],
+        input="".join(json.dumps(st) + "\n" for st in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {st['step']}" for st in steps]
+    V = model["cfg"]["vocab"]
+    outputs = {st["step"]: np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(-1, V)
+               for st in steps if any(e["want"] for e in st["entries"])}
+    _compare(model, "bfloat16", H.collect(steps, outputs, V))
 
 
 # --------------------------------------------------------------- generation
