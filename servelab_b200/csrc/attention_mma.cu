@@ -247,24 +247,35 @@ struct TalkArgs {
 // distance anyway).  (r1, r2) per row half; r1 is applied in the base-2 domain, where
 // r1 ln(x) log2(e) = r1 log2(x).
 // The accumulators are not touched here: the caller multiplies them by alpha (it may hold
-// several, one per value head).
+// several, one per value head).  The kernel is bound by the transcendental unit (an exponential
+// per score at least), so the bias costs as little of it as possible: with `tab` (per row half:
+// the row's head's bias by distance, in shared memory, or null) it is a load; without, one
+// logarithm, the distance being formed in float from constants (no conversion per score).
 template <int NT>
 __device__ __forceinline__ void softmax_tile_bias(float (&s)[NT][4], float (&alpha)[2], float (&m)[2],
                                                   float (&l)[2], int kpos0, int kend, int pos_lo,
                                                   int pos_hi, int window, float scale_log2,
-                                                  const float (&r1)[2], const float (&r2)[2]) {
+                                                  const float (&r1)[2], const float (&r2)[2],
+                                                  const float* const (&tab)[2]) {
     const int tig = threadIdx.x & 3;
     float mx[2] = {-INFINITY, -INFINITY};
+    // distance of row half h to key (j, e): dist0[h] - (j * 8 + (e & 1))
+    const int d0[2] = {pos_lo - kpos0 - tig * 2, pos_hi - kpos0 - tig * 2};
+    const float d0f[2] = {(float)d0[0], (float)d0[1]};
+    const int kleft = kend - kpos0 - tig * 2;              // key (j, e) exists iff j * 8 + (e & 1) < kleft
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int kp = kpos0 + j * 8 + tig * 2 + (e & 1);
-            const int pos = (e < 2) ? pos_lo : pos_hi;
-            const bool vis = kp < kend && kp <= pos && (window <= 0 || pos - kp < window);
-            s[j][e] = vis ? fmaf(s[j][e], scale_log2, -r1[e >> 1] * log2f(fmaf(r2[e >> 1], (float)(pos - kp), 1.f)))
-                          : -INFINITY;
-            mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+            const int off = j * 8 + (e & 1);
+            const int h = e >> 1;
+            const int dist = d0[h] - off;
+            const bool vis = off < kleft && dist >= 0 && (window <= 0 || dist < window);
+            float bias;
+            if (tab[h] != nullptr) bias = vis ? tab[h][dist] : 0.f;
+            else bias = r1[h] * __log2f(fmaf(r2[h], d0f[h] - (float)off, 1.f));
+            s[j][e] = vis ? fmaf(s[j][e], scale_log2, -bias) : -INFINITY;
+            mx[h] = fmaxf(mx[h], s[j][e]);
         }
     }
 #pragma unroll
@@ -353,9 +364,9 @@ __device__ __forceinline__ void load_k_and_value_tiles(bf16* Ks, bf16* Vs, int n
 // Value heads a block of the prefill kernel for mixed heads finishes at once: their float32
 // accumulators (16 rows x D a warp each) must fit in registers beside the scores.
 constexpr int TALK_NV = D <= 64 ? 4 : (D <= 128 ? 2 : 1);
-// Keys a tile: 32 for the large head sizes, so that two blocks (their registers allow no more)
-// also fit an SM's shared memory.
-constexpr int TALK_BN = D <= 64 ? 64 : 32;
+// Keys a tile: 32 from head size 64 on, so that two blocks (their registers allow no more)
+// also fit an SM's shared memory, the table of the bias by distance included.
+constexpr int TALK_BN = D < 64 ? 64 : 32;
 constexpr int TALK_STAGE_ELEMS = (1 + TALK_NV) * TALK_BN * LDS;
 
 // The prefill kernel for mixers with a distance bias and mixed heads: like
@@ -367,11 +378,22 @@ __global__ void __launch_bounds__(NTHREADS) talk_prefill_attention_kernel(
     const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_q,
     const int* __restrict__ ctx_len, const int* __restrict__ tile_seq, const int* __restrict__ tile_row0,
-    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, TalkArgs ta) {
+    int H, int Hkv, int ps, int num_pages, float scale_log2, int window, TalkArgs ta, int table_len) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDS]
     bf16* stage0 = Qs + BM * LDS;                          // 2 x (K tile | TALK_NV V tiles)
+    // the bias of the group's heads by distance, [g][table_len + 4] (the pad spreads a token's
+    // heads over the banks); table_len == 0: not tabulated (it would not fit)
+    float* bias_tab = reinterpret_cast<float*>(stage0 + 2 * TALK_STAGE_ELEMS);
+    const int tab_ld = table_len + 4;
+    if (table_len > 0 && ta.r1 != nullptr) {               // (weights only: before the wait)
+        const int g0 = H / Hkv, kv0 = blockIdx.x % Hkv;
+        for (int idx = threadIdx.x; idx < g0 * table_len; idx += NTHREADS) {
+            const int hg = idx / table_len, dist = idx - hg * table_len;
+            bias_tab[hg * tab_ld + dist] = ta.r1[kv0 * g0 + hg] * log2f(fmaf(ta.r2[kv0 * g0 + hg], (float)dist, 1.f));
+        }
+    }
+    pdl_wait();
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x % Hkv;
@@ -412,9 +434,14 @@ __global__ void __launch_bounds__(NTHREADS) talk_prefill_attention_kernel(
     const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
     const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
     float br1[2] = {0.f, 0.f}, br2[2] = {0.f, 0.f};
+    const float* tab[2] = {nullptr, nullptr};
     if (ta.r1 != nullptr) {
         if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + (row0 + r_lo) % g]; br2[0] = ta.r2[kvh * g + (row0 + r_lo) % g]; }
         if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + (row0 + r_hi) % g]; br2[1] = ta.r2[kvh * g + (row0 + r_hi) % g]; }
+        if (table_len > 0) {
+            tab[0] = bias_tab + ((row0 + min(r_lo, nrows - 1)) % g) * tab_ld;
+            tab[1] = bias_tab + ((row0 + min(r_hi, nrows - 1)) % g) * tab_ld;
+        }
     }
     const int wr_last = min(nrows - 1, warp * 16 + 15);
     const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
@@ -446,7 +473,7 @@ __global__ void __launch_bounds__(NTHREADS) talk_prefill_attention_kernel(
             float sc[TALK_BN / 8][4];
             qk_tile_q_in_smem<TALK_BN / 8>(sc, Qs + warp * 16 * LDS, Ks, 0);
             float alpha[2];
-            softmax_tile_bias<TALK_BN / 8>(sc, alpha, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            softmax_tile_bias<TALK_BN / 8>(sc, alpha, m, l, k0, kend, pos_lo, pos_hi, window, scale_log2, br1, br2, tab);
             const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
 #pragma unroll
             for (int j = 0; j < TALK_NV; ++j) {
@@ -882,6 +909,7 @@ __global__ void __launch_bounds__(NTHREADS) talk_decode_attention_kernel(
         if (r_lo < nrows) { br1[0] = ta.r1[kvh * g + h0 + r_lo]; br2[0] = ta.r2[kvh * g + h0 + r_lo]; }
         if (r_hi < nrows) { br1[1] = ta.r1[kvh * g + h0 + r_hi]; br2[1] = ta.r2[kvh * g + h0 + r_hi]; }
     }
+    const float* const no_tab[2] = {nullptr, nullptr};     // (a step of single tokens: one logarithm a score)
     unsigned qf[KSTEPS][4];
     float o[TALK_NV][NT_O][4];
 #pragma unroll
@@ -909,7 +937,7 @@ __global__ void __launch_bounds__(NTHREADS) talk_decode_attention_kernel(
             float sc[2][4];
             qk_tile<2>(sc, qf, Ks, warp * 16);
             float alpha[2];
-            softmax_tile_bias<2>(sc, alpha, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2);
+            softmax_tile_bias<2>(sc, alpha, m, l, k0, ctx, pos_lo, pos_hi, window, scale_log2, br1, br2, no_tab);
             const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
 #pragma unroll
             for (int j = 0; j < TALK_NV; ++j) {
@@ -1038,13 +1066,20 @@ int slb_talk_prefill_attention_bf16(const bf16* q, int ldq, const bf16* kc, cons
     if ((long long)num_tiles * Hkv > 0x7fffffffll || Hkv > 65535) return SLB_ERR_TOO_LARGE;
     static unsigned long long configured = 0;
     constexpr size_t SMEM = (size_t)(BM * LDS + 2 * TALK_STAGE_ELEMS) * sizeof(bf16);
-    const int crc = slb_configure(&configured, talk_prefill_attention_kernel, SMEM);
+    // bytes of the bias table a block may hold: what leaves room for two blocks on an SM
+    constexpr size_t TABLE_MAX = SMEM + 1024 < 112 * 1024 ? (112 * 1024 - SMEM - 1024 < 48 * 1024 ? 112 * 1024 - SMEM - 1024 : 48 * 1024) : 0;
+    const int crc = slb_configure(&configured, talk_prefill_attention_kernel, SMEM + TABLE_MAX);
     if (crc != 0) return crc;
     const int nvh = every_pair ? Hkv : 1;
+    // the bias by distance, tabulated per block where the window bounds the distances
+    const int g = H / Hkv;
+    int table_len = 0;
+    if (r1 != nullptr && window > 0 && (size_t)g * (window + 4) * sizeof(float) <= TABLE_MAX) table_len = window;
+    const size_t smem = SMEM + (table_len > 0 ? (size_t)g * (table_len + 4) * sizeof(float) : 0);
     return slb_launch(talk_prefill_attention_kernel, dim3((unsigned)num_tiles * Hkv, (nvh + TALK_NV - 1) / TALK_NV),
-                      dim3(NTHREADS), SMEM, st, q, ldq, kc, vc, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                      dim3(NTHREADS), smem, st, q, ldq, kc, vc, block_table, max_pages, cu_q, ctx_len, tile_seq,
                       tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
-                      TalkArgs{r1, r2, pair_o, nullptr, nvh});
+                      TalkArgs{r1, r2, pair_o, nullptr, nvh}, table_len);
 }
 
 // The decode kernel for mixed heads: partials pair_o float32 [S][H][nvh][splits][D] and
