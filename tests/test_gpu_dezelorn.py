@@ -434,3 +434,31 @@ def test_greedy_generation_through_the_engine(model):
     eng.runner.cache.check_invariants()
     st = eng.stats()
     assert st["running"] == 0 and st["pages_used"] == [0] * len(st["pages_used"])
+
+
+def test_command_line(model, tmp_path):
+    """``python -m servelab_b200 --model <folder>`` chooses the model class by config.json and
+    generates what the oracle generates; ``--random-weights config.json`` writes a model of the
+    design from its config alone."""
+    import json
+    import os
+    import subprocess
+    import sys
+    if model["name"] != "P":
+        pytest.skip("one configuration is enough for the command line")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pc, pw = model["plain"]
+    want = plain.greedy(pc, pw, [3, 1, 4, 1, 5], 6)
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--model", model["folder"],
+                        "--prompt-ids", "3,1,4,1,5", "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "float32", "--ignore-eos", "--block-size", "8", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert f"finish=length -> {want}" in r.stdout and "stats:" in r.stdout
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(C.R))
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--random-weights", str(cfg_path),
+                        "--prompt-ids", "1,2,3", "--max-tokens", "5", "--temperature", "0.8", "--seed", "3",
+                        "--ignore-eos", "--block-size", "4", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "finish=length" in r.stdout, r.stderr[-2000:]
