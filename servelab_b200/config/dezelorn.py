@@ -196,4 +196,7 @@ class DezelornConfig:
             final_norm=norm, tie_word_embeddings=False,
             max_position_embeddings=_MAX_POSITIONS, eos_token_ids=self.eos_token_ids,
             embed_name="embed", lm_head_name="head", final_norm_prefix="final.norm",
-            layer_prefix="l{}", ignored_suffixes=(), embedding_scale=self.embedding_scale)
+            layer_prefix="l{}", embedding_scale=self.embedding_scale,
+            # a layer without a feed-forward has no use for the norms around one; a checkpoint that
+            # stores them all the same is taken (they are declared, and so required, wherever used)
+            ignored_suffixes=(".norm2", ".norm2.b", ".norm2.alpha", ".norm2b", ".norm2b.b", ".norm2b.alpha"))

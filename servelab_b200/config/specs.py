@@ -94,8 +94,9 @@ class ConvTalkAttentionSpec(PartSpec):
     alone, with these steps, each a parameter of its own:
 
     ``conv_taps``        a causal convolution over time on every channel of the projected
-                         queries and keys (1: none); the last ``conv_taps - 1`` projected rows
-                         of a request are per-request state;
+                         queries and keys (0: none; 1: a learned factor per channel and no
+                         state); the last ``conv_taps - 1`` projected rows of a request are
+                         per-request state;
     ``tied_values``      the values are the keys as they leave the convolution (no value
                          projection, keys stored once);
     ``q_temp_coef/every`` queries at position p are multiplied by
@@ -114,7 +115,7 @@ class ConvTalkAttentionSpec(PartSpec):
     head_dim: int = 0
     window: Optional[int] = None
     scale: Optional[float] = None          # None => head_dim ** -0.5
-    conv_taps: int = 1
+    conv_taps: int = 0
     tied_values: bool = True
     q_temp_coef: Optional[float] = None
     q_temp_every: int = 1

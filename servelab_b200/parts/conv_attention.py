@@ -47,8 +47,8 @@ class ConvTalkAttention(Mixer):
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if not spec.tied_values:
             raise ValueError("conv_talk_attention: only tied values (v = k) are built")
-        if spec.conv_taps < 1 or spec.conv_taps > K.CONV_MAX_TAPS:
-            raise ValueError(f"conv_talk_attention: 1..{K.CONV_MAX_TAPS} taps, got {spec.conv_taps}")
+        if spec.conv_taps < 0 or spec.conv_taps > K.CONV_MAX_TAPS:
+            raise ValueError(f"conv_talk_attention: 0..{K.CONV_MAX_TAPS} taps, got {spec.conv_taps}")
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
@@ -66,7 +66,7 @@ class ConvTalkAttention(Mixer):
         n = cls._names(spec, prefix)
         out = [TensorDecl(n["q"], (q, h), MATRIX), TensorDecl(n["k"], (kv, h), MATRIX),
                TensorDecl(n["o"], (h, q), MATRIX)]
-        if spec.conv_taps > 1:
+        if spec.conv_taps >= 1:
             out += [TensorDecl(n["q"] + spec.conv_suffix, (q, spec.conv_taps), BIAS),
                     TensorDecl(n["k"] + spec.conv_suffix, (kv, spec.conv_taps), BIAS)]
         if spec.distance_bias:
@@ -81,7 +81,7 @@ class ConvTalkAttention(Mixer):
     @classmethod
     def cache_request(cls, spec):
         pages = PagedKVRequest(spec.num_kv_heads, spec.head_dim, spec.window, tied_values=True)
-        if spec.conv_taps == 1:
+        if spec.conv_taps <= 1:
             return pages
         width = (spec.num_heads + spec.num_kv_heads) * spec.head_dim
         return (pages, FixedStateRequest((spec.conv_taps - 1, width)))
@@ -91,7 +91,7 @@ class ConvTalkAttention(Mixer):
         n = self._names(s, self.prefix)
         self.w_in = store.cat([n["q"], n["k"]] + ([n["gate"]] if s.output_gate else []))
         self.w_o = store.get(n["o"])
-        if s.conv_taps > 1:
+        if s.conv_taps >= 1:
             # [taps, channels]: a tap's weights of neighbouring channels are neighbours
             self.taps = store.cat([n["q"] + s.conv_suffix, n["k"] + s.conv_suffix]).t().contiguous()
         else:

@@ -1,6 +1,6 @@
 """Tiny Dezelorn configurations for the tests.  They differ in every size and constant and
 include the values a model could happen to make equal or 1: one kv head, as many kv heads as
-heads, one tap (no convolution, no state), a window of one key, a window longer than any
+heads, one tap (a factor per channel, no state), a window of one key, a window longer than any
 request, a temperature that changes every few tokens, layers without a feed-forward and
 layers that differ inside one model, head sizes the tensor-core kernels take (16, 32, 64) and
 one they do not (24); a third model has sizes that fit no 16-byte access."""

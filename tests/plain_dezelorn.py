@@ -103,9 +103,8 @@ def attention_mixer(h, W, prefix, m):
     H, G, D = m["heads"], m["kv_heads"], m["dim"]
     q = h @ W[prefix + "q"].T
     k = h @ W[prefix + "k"].T
-    if m["conv"] > 1:
-        q = causal_conv(q, W[prefix + "q.conv"])
-        k = causal_conv(k, W[prefix + "k.conv"])
+    q = causal_conv(q, W[prefix + "q.conv"])            # (one tap: a factor per channel)
+    k = causal_conv(k, W[prefix + "k.conv"])
     q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"], h.dtype)[:, None]
     q, k = q.view(T, H, D), k.view(T, G, D)
     w = attention_weights(q, k, m["scale"], W[prefix + "r1"], W[prefix + "r2"], m["mask"]["size"])

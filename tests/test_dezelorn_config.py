@@ -65,7 +65,7 @@ def test_declared_tensors():
     assert decls["l0.mix.r1"] == (6,) and decls["l0.mix.talk"] == (6, 6)
     assert decls["l0.mlp.gate"] == (72, 48) and decls["l0.mlp.down"] == (48, 72)
     assert "l1.mlp.gate" not in decls and "l1.norm2" not in decls and "l1.norm1b.alpha" in decls
-    assert "l2.mix.q.conv" not in decls                       # one tap: no convolution
+    assert decls["l2.mix.q.conv"] == (64, 1) and decls["l2.mix.k.conv"] == (64, 1)     # one tap: a factor per channel
 
 
 def test_cache_requests_pages_with_tied_values_and_a_state_record():
@@ -73,7 +73,7 @@ def test_cache_requests_pages_with_tied_values_and_a_state_record():
     reqs = [part_class(BLOCKS, b).cache_request(b) for b in spec.layers]
     pages, state = reqs[0]
     assert pages == PagedKVRequest(3, 16, 12, tied_values=True) and state == FixedStateRequest((2, 144))
-    assert reqs[2] == PagedKVRequest(4, 16, 1000, tied_values=True)          # one tap: no record
+    assert reqs[2] == PagedKVRequest(4, 16, 1000, tied_values=True)          # one tap: a factor per channel, no record
     groups, of_layer = plan_groups(reqs)
     assert len(groups) == 3 and of_layer == {0: 0, 1: 1, 2: 2}
     assert bytes_per_page(groups, 8, torch.bfloat16) == (3 * 16 + 32 + 4 * 16) * 8 * 2   # keys only
