@@ -20,7 +20,7 @@
 // blocks may still read the old record, so a second, small kernel writes it afterwards.
 #include "common.cuh"
 
-#define SC_MAX_TAPS 16
+#define SC_MAX_TAPS 64
 
 SLB_DEFINE_STATUS_WORD(conv_cache_status_word, slb_conv_cache_status)
 

@@ -349,7 +349,7 @@ def qk_conv_cache(proj: torch.Tensor, taps_w: torch.Tensor, state: Optional[torc
     launch_count += n - 1
 
 
-CONV_MAX_TAPS = 16             # taps of the short convolution the kernel holds in registers
+CONV_MAX_TAPS = 64             # most taps the convolution kernel is launched with
 
 
 def conv_cache_status(reset: bool = False) -> int:

@@ -88,7 +88,7 @@ def test_product_with_both_norms_in_its_epilogue(M):
 # ----------------------------------------------------- convolution + cache
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("D", [8, 6])
-@pytest.mark.parametrize("taps", [1, 2, 4, 7])
+@pytest.mark.parametrize("taps", [1, 2, 4, 7, 20])
 def test_conv_kernel_over_portions_and_single_tokens(dtype, taps, D):
     """Two requests fed in unequal portions (one of them of single tokens from the start, so
     the state is shifted on the spot) give the convolution of their whole sequences; keys land
