@@ -33,11 +33,14 @@ class PagedKVRequest:
     """Keys and values of ``num_kv_heads`` x ``head_dim`` per token, paged.
     ``window`` None: all earlier tokens stay readable; else only the last
     ``window`` positions (the current one included).  ``tied_values``: the values are
-    the keys themselves, so only keys are stored (``LayerCache.v`` is ``LayerCache.k``)."""
+    the keys themselves (or a prefix of every key row), so only keys are stored
+    (``LayerCache.v`` is ``LayerCache.k``).  ``value_dim``: the size of a value row where it
+    differs from the keys' ``head_dim`` (None: the same)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     tied_values: bool = False
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -52,8 +52,9 @@ def plan_groups(requests: Sequence[Optional[object]]) -> Tuple[List[GroupPlan], 
 def bytes_per_page(groups: Sequence[GroupPlan], page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page costs when every group gets the same number of pages."""
     el = torch.empty((), dtype=dtype).element_size()
-    return sum((1 if g.request.tied_values else 2) * len(g.layers) * g.request.num_kv_heads
-               * g.request.head_dim * page_size * el for g in groups)
+    return sum(len(g.layers) * g.request.num_kv_heads * page_size * el *
+               (g.request.head_dim + (0 if g.request.tied_values else (g.request.value_dim or g.request.head_dim)))
+               for g in groups)
 
 
 def pages_from_memory(groups, page_size, dtype, free_bytes: int, utilization: float) -> int:
@@ -85,9 +86,21 @@ class CacheStorage:
         self._buffers = []
         for gi, g in enumerate(self.groups):
             r = g.request
+            fill = POISON if poison else 0.0
+            if r.value_dim is not None and r.value_dim != r.head_dim and not r.tied_values:
+                # keys and values of two sizes: a buffer each, [layer][page][kv head][slot][size]
+                kbuf = torch.full((len(g.layers), 1, num_pages, r.num_kv_heads, page_size, r.head_dim),
+                                  fill, dtype=dtype, device=device)
+                vbuf = torch.full((len(g.layers), 1, num_pages, r.num_kv_heads, page_size, r.value_dim),
+                                  fill, dtype=dtype, device=device)
+                self._buffers.append([kbuf, vbuf])
+                for li, layer in enumerate(g.layers):
+                    self.layer_caches[layer] = LayerCache(group=gi, k=kbuf[li, 0], v=vbuf[li, 0],
+                                                          page_size=page_size)
+                continue
             buf = torch.full((len(g.layers), 1 if r.tied_values else 2, num_pages, r.num_kv_heads,
-                              page_size, r.head_dim), POISON if poison else 0.0, dtype=dtype, device=device)
-            self._buffers.append(buf)
+                              page_size, r.head_dim), fill, dtype=dtype, device=device)
+            self._buffers.append([buf])
             for li, layer in enumerate(g.layers):
                 self.layer_caches[layer] = LayerCache(group=gi, k=buf[li, 0], v=buf[li, -1],
                                                       page_size=page_size)
@@ -135,10 +148,11 @@ class CacheStorage:
         """Debugging mode: pages that went back to the free list hold ``POISON`` again."""
         if not self.poison or not pages:
             return
-        buf = self._buffers[group]
-        idx = torch.tensor(list(pages), dtype=torch.long, device=buf.device)
-        buf.index_fill_(2, idx, POISON)
+        bufs = self._buffers[group]
+        idx = torch.tensor(list(pages), dtype=torch.long, device=bufs[0].device)
+        for buf in bufs:
+            buf.index_fill_(2, idx, POISON)
 
     def nbytes(self) -> int:
-        n = sum(b.numel() * b.element_size() for b in self._buffers)
+        n = sum(b.numel() * b.element_size() for bufs in self._buffers for b in bufs)
         return n + sum(self.layer_caches[l].state.numel() * 4 for l in self.state_layers)

@@ -1,22 +1,27 @@
 """Typed configuration: model specs as data, family configs, engine knobs."""
 
 from .engine import CacheConfig, EngineConfig, SchedulerConfig
+from .daferax import DaferaxConfig
 from .dezelorn import DezelornConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .registry import (config_from_dict, load_config, model_spec_from_config,
                        register_architecture, registered_architectures,
                        resolve_architecture)
 from .specs import (AttentionSpec, BlockSpec, ConvTalkAttentionSpec, DynamicTanhSpec, GatedMLPSpec,
-                    LayerRun, ModelSpec, NoPositionSpec, PartSpec, RMSNormSpec, RotarySpec)
+                    LatentAttentionSpec, LayerNormSpec, LayerRun, ModelSpec, NoPositionSpec,
+                    NormedAttentionSpec, PairRotarySpec, PartSpec, RMSNormSpec, RotarySpec,
+                    RoutedExpertsSpec)
 
 register_architecture(Qwen2Config.architecture, Qwen2Config, model_type=Qwen2Config.model_type)
 register_architecture(DezelornConfig.architecture, DezelornConfig, model_type=DezelornConfig.model_type)
+register_architecture(DaferaxConfig.architecture, DaferaxConfig, model_type=DaferaxConfig.model_type)
 
 __all__ = [
     "AttentionSpec", "BlockSpec", "CacheConfig", "ConfigError", "ConvTalkAttentionSpec",
-    "DezelornConfig", "DynamicTanhSpec", "EngineConfig",
-    "GatedMLPSpec", "LayerRun", "ModelSpec", "NoPositionSpec", "PartSpec",
-    "Qwen2Config", "RMSNormSpec", "RotarySpec", "SchedulerConfig",
+    "DaferaxConfig", "DezelornConfig", "DynamicTanhSpec", "EngineConfig",
+    "GatedMLPSpec", "LatentAttentionSpec", "LayerNormSpec", "LayerRun", "ModelSpec", "NoPositionSpec",
+    "NormedAttentionSpec", "PairRotarySpec", "PartSpec",
+    "Qwen2Config", "RMSNormSpec", "RotarySpec", "RoutedExpertsSpec", "SchedulerConfig",
     "config_from_dict", "load_config", "model_spec_from_config",
     "register_architecture", "registered_architectures", "resolve_architecture",
 ]

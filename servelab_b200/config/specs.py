@@ -41,12 +41,39 @@ class NoPositionSpec(PartSpec):
     kind: str = "none"
 
 
+@dataclass(frozen=True)
+class PairRotarySpec(PartSpec):
+    """Rotary encoding that pairs NEIGHBOURING elements (2i with 2i + 1) of ``dims`` elements of
+    a head, frequencies f_i = theta^(-2i / dims).  With ``yarn_factor`` the frequencies are
+    interpolated between f_i and f_i / factor by a ramp over i that runs from the pair that
+    turns ``yarn_fast`` times within ``yarn_original`` positions to the one that turns
+    ``yarn_slow`` times, and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    kind: str = "rotary_pairs"
+    dims: int = 0
+    theta: float = 10000.0
+    yarn_factor: Optional[float] = None
+    yarn_original: float = 0.0
+    yarn_fast: float = 32.0
+    yarn_slow: float = 1.0
+
+
 # --------------------------------------------------------------------- norms
 @dataclass(frozen=True)
 class RMSNormSpec(PartSpec):
     kind: str = "rmsnorm"
     dim: int = 0
     eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class LayerNormSpec(PartSpec):
+    """(x - mean) / sqrt(var + eps) * w + b over a row; tensors ``<prefix><weight_suffix>`` and
+    ``<prefix><bias_suffix>``."""
+    kind: str = "layernorm"
+    dim: int = 0
+    eps: float = 1e-5
+    weight_suffix: str = ".weight"
+    bias_suffix: str = ".bias"
 
 
 @dataclass(frozen=True)
@@ -134,6 +161,74 @@ class ConvTalkAttentionSpec(PartSpec):
     weight_suffix: str = ""
 
 
+@dataclass(frozen=True)
+class NormedAttentionSpec(PartSpec):
+    """Grouped-query softmax attention whose keys and values may differ in size, with these
+    steps, each a parameter:
+
+    ``qk_norm``      RMS norm over every query and key head before the rotation, one weight
+                     vector per projection shared by the heads (``qk_norm_eps``);
+    ``position``     a ``PairRotarySpec`` on the first ``dims`` elements of a head, or none;
+    ``value_mix``    None; "source": this layer's values (before any mixing) are kept for the
+                     step; "mix": v <- (1 - lambda) v + lambda v_source with a learned scalar,
+                     the mixed values being what the cache holds.  ``value_mix_key`` names the
+                     source among the layers of a model;
+    ``head_gate``    head h's result is multiplied by sigmoid((W_g x)_h), one number a head;
+    ``window``       None: every earlier key; else the last ``window`` keys (own included).
+    """
+    kind: str = "normed_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0                      # queries and keys
+    value_dim: int = 0
+    window: Optional[int] = None
+    scale: Optional[float] = None          # None => head_dim ** -0.5
+    qk_norm: bool = False
+    qk_norm_eps: float = 1e-6
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    value_mix: Optional[str] = None
+    value_mix_key: str = "v_first"
+    head_gate: bool = False
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    o_name: str = "o"
+    gate_name: str = "g"
+    q_norm_name: str = "q.norm"
+    k_norm_name: str = "k.norm"
+    value_mix_name: str = "vmix"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Attention whose keys and values are expanded from one latent vector per token: the
+    product W_dkv x gives ``kv_rank`` latent elements (RMS-normed, ``latent_norm_eps``) and
+    ``rope_dim`` elements of a rotated key part that all heads share; head h's unrotated key is
+    W_uk[h] c and its value W_uv[h] c.  A query head is [``head_dim`` unrotated | ``rope_dim``
+    rotated].  Only the latent and the rotated part are cached.  ``element_gate``: the
+    concatenated heads are multiplied by sigmoid(W_g x)."""
+    kind: str = "latent_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0                      # unrotated part of queries and keys
+    rope_dim: int = 0
+    value_dim: int = 0
+    kv_rank: int = 0
+    window: Optional[int] = None
+    scale: Optional[float] = None          # None => (head_dim + rope_dim) ** -0.5
+    latent_norm_eps: float = 1e-6
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    element_gate: bool = False
+    q_name: str = "q"
+    down_name: str = "dkv"
+    latent_norm_name: str = "dkv.norm"
+    up_k_name: str = "uk"
+    up_v_name: str = "uv"
+    o_name: str = "o"
+    gate_name: str = "g"
+
+
 # -------------------------------------------------------------- feed-forward
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
@@ -149,6 +244,33 @@ class GatedMLPSpec(PartSpec):
     weight_suffix: str = ".weight"         # a matrix is <prefix>.<name><weight_suffix>
 
 
+@dataclass(frozen=True)
+class RoutedExpertsSpec(PartSpec):
+    """``num_experts`` gated feed-forwards of which a token uses ``top``: scores = softmax of the
+    router's float32 logits over all experts; the experts form ``num_groups`` equal groups of
+    neighbours, a group scores as its best expert and only the ``keep_groups`` best groups'
+    experts can be chosen; the chosen experts' outputs are weighted by their scores times
+    ``route_scale`` (divided by the sum of the chosen scores first with ``renormalize``).
+    ``shared``: a dense gated feed-forward that every token also passes, added to the sum."""
+    kind: str = "routed_experts"
+    hidden_size: int = 0
+    num_experts: int = 0
+    top: int = 1
+    expert_size: int = 0
+    num_groups: int = 1
+    keep_groups: int = 1
+    route_scale: float = 1.0
+    renormalize: bool = False
+    shared: Optional[PartSpec] = None
+    router_name: str = "router"
+    expert_prefix: str = "e{}"             # expert j's tensors: <prefix>.e<j>.<gate|up|down>
+    gate_name: str = "gate"
+    up_name: str = "up"
+    down_name: str = "down"
+    shared_name: str = "shared"
+    weight_suffix: str = ""
+
+
 # --------------------------------------------------------------------- block
 @dataclass(frozen=True)
 class BlockSpec(PartSpec):
@@ -156,7 +278,9 @@ class BlockSpec(PartSpec):
     ``pre_norm`` is x += mixer(norm1(x)); x += ff(norm2(x)).
     ``sandwich_norm`` norms each sublayer's result as well before it is added:
     x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))); its ``feed_forward`` may be
-    None (a layer that has a mixer only)."""
+    None (a layer that has a mixer only).
+    ``result_norm`` norms only what a sublayer returns; the sublayers read the stream itself:
+    x += norm1(mixer(x)); x += norm2(ff(x)) (``mixer_post_norm``, ``ff_post_norm``)."""
     kind: str = "pre_norm"
     mixer: PartSpec = None
     feed_forward: PartSpec = None

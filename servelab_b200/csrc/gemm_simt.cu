@@ -18,9 +18,13 @@
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(
     const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw, TC* __restrict__ C,
-    int ldc, const float* __restrict__ bias, int M, int N, int K) {
+    int ldc, const float* __restrict__ bias, int M, int N, int K, long long batch_a,
+    long long batch_w, long long batch_c) {
     __shared__ __align__(16) float As[GS_BK][GS_BM + 4];
     pdl_wait();
+    A += (size_t)blockIdx.z * batch_a;          // a batch of products: one per grid z
+    W += (size_t)blockIdx.z * batch_w;
+    C += (size_t)blockIdx.z * batch_c;
     __shared__ __align__(16) float Ws[GS_BK][GS_BN + 4];
     const int tid = threadIdx.x;
     const int ty = tid >> 4, tx = tid & 15;
@@ -69,13 +73,14 @@ __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(
 
 template <typename TA, typename TW, typename TC>
 static int launch_gemm(const TA* A, int lda, const TW* W, int ldw, TC* C, int ldc,
-                       const float* bias, int M, int N, int K, cudaStream_t st) {
-    if (M <= 0 || N <= 0) return 0;
+                       const float* bias, int M, int N, int K, cudaStream_t st, int batch = 1,
+                       long long batch_a = 0, long long batch_w = 0, long long batch_c = 0) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
     if (K <= 0 || lda < K || ldw < K || ldc < N) return SLB_ERR_BAD_ARG;
     const int gy = (M + GS_BM - 1) / GS_BM;
-    if (gy > 65535) return SLB_ERR_TOO_LARGE;
-    return slb_launch(gemm_tn_simt_kernel<TA, TW, TC>, dim3((N + GS_BN - 1) / GS_BN, gy), dim3(256),
-                      0, st, A, lda, W, ldw, C, ldc, bias, M, N, K);
+    if (gy > 65535 || batch > 65535) return SLB_ERR_TOO_LARGE;
+    return slb_launch(gemm_tn_simt_kernel<TA, TW, TC>, dim3((N + GS_BN - 1) / GS_BN, gy, batch), dim3(256),
+                      0, st, A, lda, W, ldw, C, ldc, bias, M, N, K, batch_a, batch_w, batch_c);
 }
 
 extern "C" {
@@ -86,6 +91,25 @@ int slb_gemm_simt_f32(const float* A, int lda, const float* W, int ldw, float* C
 int slb_gemm_simt_bf16(const bf16* A, int lda, const bf16* W, int ldw, bf16* C, int ldc,
                        const float* bias, int M, int N, int K, cudaStream_t st) {
     return launch_gemm<bf16, bf16, bf16>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
+}
+// `batch` products in one launch: product b reads A + b * batch_a, W + b * batch_w and writes
+// C + b * batch_c (element strides; the per-head products of a latent attention).
+int slb_gemm_simt_batched_f32(const float* A, int lda, const float* W, int ldw, float* C, int ldc, int M,
+                              int N, int K, int batch, long long batch_a, long long batch_w,
+                              long long batch_c, cudaStream_t st) {
+    return launch_gemm<float, float, float>(A, lda, W, ldw, C, ldc, nullptr, M, N, K, st, batch, batch_a,
+                                            batch_w, batch_c);
+}
+int slb_gemm_simt_batched_bf16(const bf16* A, int lda, const bf16* W, int ldw, bf16* C, int ldc, int M,
+                               int N, int K, int batch, long long batch_a, long long batch_w,
+                               long long batch_c, cudaStream_t st) {
+    return launch_gemm<bf16, bf16, bf16>(A, lda, W, ldw, C, ldc, nullptr, M, N, K, st, batch, batch_a,
+                                         batch_w, batch_c);
+}
+// bfloat16 activations against a float32 matrix, float32 result (a router's logits)
+int slb_gemm_simt_bf16_wf32(const bf16* A, int lda, const float* W, int ldw, float* C, int ldc,
+                            const float* bias, int M, int N, int K, cudaStream_t st) {
+    return launch_gemm<bf16, float, float>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
 }
 int slb_gemm_simt_bf16_f32out(const bf16* A, int lda, const bf16* W, int ldw, float* C, int ldc,
                               const float* bias, int M, int N, int K, cudaStream_t st) {

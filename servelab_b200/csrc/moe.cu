@@ -1,0 +1,336 @@
+// Routed experts: the router's choice, the plan of a step (which rows each expert gets), the
+// experts' products on CUDA cores, and the weighted sum.
+//
+//   slb_moe_route      scores = softmax(logits) in float32 per token; experts form `groups` equal
+//                      groups of neighbours, a group's score is its largest score, only experts of
+//                      the `keep` best groups can be chosen; the `top` largest scores among those
+//                      are the choice (ties: the lower index); weight = score * route_scale
+//                      (optionally divided by the sum of the chosen scores).
+//   slb_moe_plan       (token, choice) pairs sorted by expert: counts, offsets, the list, and the
+//                      row tiles of the products (tile -> expert, first row), of a length that
+//                      depends only on the number of pairs and experts (a fixed grid).
+//   slb_moe_gate_up    act[pair] = silu(W_gate[e] x) * (W_up[e] x) for the pair's expert e;
+//   slb_moe_down       y[pair] = W_down[e] act[pair], float32;
+//   slb_moe_combine    out[t] = (shared[t]) + sum_k weight[t][k] * y[t * top + k], in the order k.
+//
+// Each output element of a product is a sum over k = 0..K-1 in that order (plain FFMA), and the
+// combine adds a token's experts in the order of its choice, so a token's result does not depend
+// on what else is in the batch.
+#include "common.cuh"
+
+#define MOE_MAX_EXPERTS 1024
+#define MOE_MAX_TOP 32
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+
+// ------------------------------------------------------------------- route
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) {
+            v = ov;
+            i = oi;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_route_kernel(
+    const float* __restrict__ logits, int ldl, int T, int E, int groups, int keep, int top,
+    float route_scale, int renormalize, int* __restrict__ ids, float* __restrict__ weights) {
+    extern __shared__ float route_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= T) return;
+    float* s = route_smem + (size_t)warp * (E + groups);      // scores, then the groups' scores
+    float* gs = s + E;
+    const float* z = logits + (size_t)t * ldl;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(z[e] - mx);
+        s[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) s[e] *= inv;
+    __syncwarp();
+    const int per = E / groups;
+    if (groups > 1) {
+        for (int g = lane; g < groups; g += 32) {
+            float b = -1.f;
+            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, s[e]);
+            gs[g] = b;
+        }
+        __syncwarp();
+        // the `keep` best groups get the mark 2 (a score is at most 1)
+        for (int round = 0; round < keep; ++round) {
+            float bv = -1.f;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (gs[g] <= 1.5f && (gs[g] > bv || (gs[g] == bv && g < bi))) {
+                    bv = gs[g];
+                    bi = g;
+                }
+            warp_argmax(bv, bi);
+            if (lane == 0) gs[bi] = 2.f;
+            __syncwarp();
+        }
+    }
+    float chosen_sum = 0.f;
+    for (int round = 0; round < top; ++round) {
+        float bv = -1.f;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const bool ok = groups <= 1 || gs[e / per] > 1.5f;
+            if (ok && s[e] >= 0.f && (s[e] > bv || (s[e] == bv && e < bi))) {
+                bv = s[e];
+                bi = e;
+            }
+        }
+        warp_argmax(bv, bi);
+        if (lane == 0) {
+            ids[(size_t)t * top + round] = bi;
+            weights[(size_t)t * top + round] = bv;
+            s[bi] = -1.f;                                  // taken
+        }
+        chosen_sum += bv;
+        __syncwarp();
+    }
+    if (lane < top) {
+        float w = weights[(size_t)t * top + lane];
+        if (renormalize) w /= chosen_sum;
+        weights[(size_t)t * top + lane] = w * route_scale;
+    }
+}
+
+// -------------------------------------------------------------------- plan
+// One block.  plan = [counts E | offsets E + 1 | cursor E | tile_expert NT | tile_row0 NT |
+// sorted P] (int32), NT = ceil(P / MOE_BM) + E.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int P, int E,
+                                                        int num_tiles, int* __restrict__ plan) {
+    pdl_wait();
+    pdl_launch_dependents();
+    int* counts = plan;
+    int* offsets = plan + E;
+    int* cursor = offsets + E + 1;
+    int* tile_expert = cursor + E;
+    int* tile_row0 = tile_expert + num_tiles;
+    int* sorted = tile_row0 + num_tiles;
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += blockDim.x) counts[e] = 0;
+    for (int i = tid; i < num_tiles; i += blockDim.x) tile_expert[i] = -1;
+    __syncthreads();
+    for (int p = tid; p < P; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int off = 0, tile = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = off;
+            cursor[e] = off;
+            const int n = counts[e];
+            for (int r0 = 0; r0 < n; r0 += MOE_BM, ++tile) {
+                tile_expert[tile] = e;
+                tile_row0[tile] = r0;
+            }
+            off += n;
+        }
+        offsets[E] = off;
+    }
+    __syncthreads();
+    // (a product's result is written per pair, so the order within an expert changes no value)
+    for (int p = tid; p < P; p += blockDim.x) {
+        const int e = ids[p];
+        if (e < 0 || e >= E) continue;
+        sorted[atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+// ---------------------------------------------------------------- products
+// MODE 0: gate|up with the activation: A rows are x[pair / top], W = w_gu[e] ([2 I, K]: I gate
+// rows, then I up rows), C = act[pair][I].  MODE 1: down: A rows are act[pair], W = w_down[e]
+// ([N, K = I]), C = y[pair][N] float32.
+template <typename T, typename TC, int MODE>
+__global__ void __launch_bounds__(256) moe_product_kernel(
+    const T* __restrict__ A, int lda, const T* __restrict__ W, long long w_expert_stride, int ldw,
+    TC* __restrict__ C, int ldc, const int* __restrict__ plan, int E, int num_tiles, int P, int top,
+    int N, int K) {
+    __shared__ __align__(16) float As[MOE_BK][MOE_BM + 4];
+    __shared__ __align__(16) float Ws[MOE_BK][MOE_BN + 4];
+    __shared__ __align__(16) float Us[MODE == 0 ? MOE_BK : 1][MOE_BN + 4];
+    __shared__ int rows[MOE_BM];
+    pdl_wait();
+    const int* counts = plan;
+    const int* offsets = plan + E;
+    const int* tile_expert = offsets + E + 1 + E;
+    const int* tile_row0 = tile_expert + num_tiles;
+    const int* sorted = tile_row0 + num_tiles;
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    const int r0 = tile_row0[blockIdx.y];
+    const int nrows = min(MOE_BM, counts[e] - r0);
+    const int tid = threadIdx.x;
+    if (tid < MOE_BM) rows[tid] = tid < nrows ? sorted[offsets[e] + r0 + tid] : -1;
+    __syncthreads();
+    const T* We = W + (size_t)e * w_expert_stride;
+    const int ty = tid >> 4, tx = tid & 15;
+    const int n0 = blockIdx.x * MOE_BN;
+    float acc[4][4], acu[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = acu[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256;
+            const int row = idx >> 4, kk = idx & 15;
+            const int gk = k0 + kk, gn = n0 + row;
+            const int pr = rows[row];
+            float av = 0.f;
+            if (pr >= 0 && gk < K) av = to_float(A[(size_t)(MODE == 0 ? pr / top : pr) * lda + gk]);
+            As[kk][row] = av;
+            const bool in = gn < N && gk < K;
+            Ws[kk][row] = in ? to_float(We[(size_t)gn * ldw + gk]) : 0.f;
+            if (MODE == 0) Us[kk][row] = in ? to_float(We[(size_t)(N + gn) * ldw + gk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&Ws[kk][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w};
+            const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+            if (MODE == 0) {
+                const float4 u = *reinterpret_cast<const float4*>(&Us[kk][tx * 4]);
+                const float uv[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acu[i][j] = fmaf(av[i], uv[j], acu[i][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int pr = rows[ty * 4 + i];
+        if (pr < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            float v = acc[i][j];
+            if (MODE == 0) {
+                // the gate and the up value are rounded to the activations' type first, as two
+                // separate products would leave them
+                const float gte = to_float(from_float<T>(v)), up = to_float(from_float<T>(acu[i][j]));
+                v = gte / (1.0f + expf(-gte)) * up;
+            }
+            C[(size_t)pr * ldc + gn] = from_float<TC>(v);
+        }
+    }
+}
+
+// ----------------------------------------------------------------- combine
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(
+    const float* __restrict__ y, int ldy, const float* __restrict__ weights, const T* __restrict__ shared,
+    int lds, T* __restrict__ out, int ldo, int top, int N) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < N; c += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < top; ++k) v += weights[(size_t)t * top + k] * y[((size_t)t * top + k) * ldy + c];
+        if (shared != nullptr) v += to_float(shared[(size_t)t * lds + c]);
+        out[(size_t)t * ldo + c] = from_float<T>(v);
+    }
+}
+
+static int moe_num_tiles(int P, int E) { return (P + MOE_BM - 1) / MOE_BM + E; }
+
+template <typename T>
+static int launch_moe_gate_up(const T* x, int ldx, const T* w_gu, int ldw, T* act, int lda,
+                              const int* plan, int E, int P, int top, int I, int K, cudaStream_t st) {
+    if (P <= 0) return 0;
+    if (E <= 0 || top <= 0 || I <= 0 || K <= 0) return SLB_ERR_BAD_ARG;
+    const int nt = moe_num_tiles(P, E);
+    if (nt > 65535) return SLB_ERR_TOO_LARGE;
+    return slb_launch(moe_product_kernel<T, T, 0>, dim3((I + MOE_BN - 1) / MOE_BN, nt), dim3(256), 0, st, x,
+                      ldx, w_gu, (long long)2 * I * ldw, ldw, act, lda, plan, E, nt, P, top, I, K);
+}
+
+template <typename T>
+static int launch_moe_down(const T* act, int lda, const T* w_down, int ldw, float* y, int ldy,
+                           const int* plan, int E, int P, int top, int N, int I, cudaStream_t st) {
+    if (P <= 0) return 0;
+    if (E <= 0 || top <= 0 || I <= 0 || N <= 0) return SLB_ERR_BAD_ARG;
+    const int nt = moe_num_tiles(P, E);
+    if (nt > 65535) return SLB_ERR_TOO_LARGE;
+    return slb_launch(moe_product_kernel<T, float, 1>, dim3((N + MOE_BN - 1) / MOE_BN, nt), dim3(256), 0, st,
+                      act, lda, w_down, (long long)N * ldw, ldw, y, ldy, plan, E, nt, P, top, N, I);
+}
+
+extern "C" {
+int slb_moe_tile_rows() { return MOE_BM; }
+int slb_moe_route(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
+                  float route_scale, int renormalize, int* ids, float* weights, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (E <= 0 || groups <= 0 || E % groups != 0 || keep <= 0 || keep > groups || top <= 0 ||
+        top > (E / groups) * keep)
+        return SLB_ERR_BAD_ARG;
+    if (E > MOE_MAX_EXPERTS || top > MOE_MAX_TOP) return SLB_ERR_TOO_LARGE;
+    const size_t smem = (size_t)4 * (E + groups) * sizeof(float);
+    return slb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, logits, ldl, T, E, groups,
+                      keep, top, route_scale, renormalize, ids, weights);
+}
+int slb_moe_plan_ints(int P, int E) { return 4 * E + 1 + 2 * moe_num_tiles(P, E) + P; }
+int slb_moe_plan(const int* ids, int P, int E, int* plan, cudaStream_t st) {
+    if (P <= 0) return 0;
+    if (E <= 0 || E > MOE_MAX_EXPERTS) return SLB_ERR_BAD_ARG;
+    return slb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, st, ids, P, E, moe_num_tiles(P, E), plan);
+}
+int slb_moe_gate_up_f32(const float* x, int ldx, const float* w_gu, int ldw, float* act, int lda,
+                        const int* plan, int E, int P, int top, int I, int K, cudaStream_t st) {
+    return launch_moe_gate_up<float>(x, ldx, w_gu, ldw, act, lda, plan, E, P, top, I, K, st);
+}
+int slb_moe_gate_up_bf16(const bf16* x, int ldx, const bf16* w_gu, int ldw, bf16* act, int lda,
+                         const int* plan, int E, int P, int top, int I, int K, cudaStream_t st) {
+    return launch_moe_gate_up<bf16>(x, ldx, w_gu, ldw, act, lda, plan, E, P, top, I, K, st);
+}
+int slb_moe_down_f32(const float* act, int lda, const float* w_down, int ldw, float* y, int ldy,
+                     const int* plan, int E, int P, int top, int N, int I, cudaStream_t st) {
+    return launch_moe_down<float>(act, lda, w_down, ldw, y, ldy, plan, E, P, top, N, I, st);
+}
+int slb_moe_down_bf16(const bf16* act, int lda, const bf16* w_down, int ldw, float* y, int ldy,
+                      const int* plan, int E, int P, int top, int N, int I, cudaStream_t st) {
+    return launch_moe_down<bf16>(act, lda, w_down, ldw, y, ldy, plan, E, P, top, N, I, st);
+}
+int slb_moe_combine_f32(const float* y, int ldy, const float* weights, const float* shared, int lds,
+                        float* out, int ldo, int T, int top, int N, cudaStream_t st) {
+    if (T <= 0) return 0;
+    return slb_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, st, y, ldy, weights, shared, lds,
+                      out, ldo, top, N);
+}
+int slb_moe_combine_bf16(const float* y, int ldy, const float* weights, const bf16* shared, int lds,
+                         bf16* out, int ldo, int T, int top, int N, cudaStream_t st) {
+    if (T <= 0) return 0;
+    return slb_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, st, y, ldy, weights, shared, lds,
+                      out, ldo, top, N);
+}
+}

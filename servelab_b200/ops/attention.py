@@ -95,3 +95,26 @@ def talk_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, s
     K.paged_attention_generic(q, k_cache, v_cache, None, table, ctx.cu_q, ctx.ctx_len, tile_seq,
                               tile_row0, n, H, Hkv, D, page_size, scale, window, bias_r1, bias_r2, pairs)
     K.mix_heads_gate(pairs, None, talk, gate, out, H, Hkv, D)
+
+
+# ------------------------------- attention with keys and values of two sizes
+KV_MAX_KEY_DIM, KV_MAX_VALUE_DIM = 640, 512
+
+
+def check_kv_supported(key_dim: int, value_dim: int) -> None:
+    if not 0 < key_dim <= KV_MAX_KEY_DIM or not 0 < value_dim <= KV_MAX_VALUE_DIM:
+        raise L.KernelError(f"attention kernels take keys of 1..{KV_MAX_KEY_DIM} and values of "
+                            f"1..{KV_MAX_VALUE_DIM} elements, got {key_dim} and {value_dim}")
+
+
+def prepare_kv_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> None:
+    """Builds what ``kv_attention`` will launch for these sizes (at load, not in a step)."""
+
+
+def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
+                 window, head_gate) -> None:
+    """Attention with keys of ``Dk`` and values of ``Dv`` elements (value rows ``v_row_stride``
+    apart in ``v_cache``, which may be the key cache), causal with an optional window, head h's
+    row times sigmoid(head_gate[t, h]) if given."""
+    K.attention_kv(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
+                   window, head_gate)

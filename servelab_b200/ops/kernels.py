@@ -806,3 +806,178 @@ def gemm_tc_status(reset: bool = False) -> int:
     """0 unless a bounded wait inside the tcgen05 kernels ran out, or the q|k|v epilogue met a
     block-table entry outside the cache (synchronises)."""
     return L.core().slb_gemm_tc_status(1 if reset else 0)
+
+
+# ------------------------------------------- layer norm around the residual add
+def ln_add_norm(resid: torch.Tensor, delta: Optional[torch.Tensor], post, pre,
+                out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> None:
+    """x = resid (+ LN_post(delta)); resid = x unless ``rows`` selects rows; out = LN_pre(x) or,
+    without ``pre``, x in ``out``'s dtype.  ``post`` / ``pre``: (weight, bias, eps) float32, or
+    None.  Layer norm: mean and variance over the row, float32."""
+    dt = out.dtype if out is not None else delta.dtype
+    fn = getattr(L.core(), "slb_ln_add_norm_" + _suffix(dt))
+    n = (rows.numel() if rows is not None else resid.shape[0])
+    pw, pb, pe = post if post is not None else (None, None, 0.0)
+    qw, qb, qe = pre if pre is not None else (None, None, 0.0)
+    L.check(fn(resid.data_ptr(), resid.stride(0), _p(delta), delta.stride(0) if delta is not None else 0,
+               _p(pw), _p(pb), float(pe), _p(qw), _p(qb), float(qe), _p(out),
+               out.stride(0) if out is not None else 0, _p(rows), n, resid.shape[1], _stream()),
+            "ln_add_norm")
+
+
+# ------------------------------- head norms, pair rotation, value mix, cache write
+import ctypes as _ct
+
+
+class _HeadPrepArgs(_ct.Structure):
+    _fields_ = [
+        ("proj", _ct.c_void_p), ("ld", _ct.c_int),
+        ("q_off", _ct.c_int), ("H", _ct.c_int), ("Dq", _ct.c_int), ("q_norm_dims", _ct.c_int),
+        ("q_rot_off", _ct.c_int), ("q_norm_w", _ct.c_void_p),
+        ("k_off", _ct.c_int), ("G", _ct.c_int), ("Dk", _ct.c_int), ("k_norm_dims", _ct.c_int),
+        ("k_rot_off", _ct.c_int), ("k_norm_w", _ct.c_void_p),
+        ("v_off", _ct.c_int), ("Dv", _ct.c_int),
+        ("lam", _ct.c_void_p), ("v_first", _ct.c_void_p), ("ld_vf", _ct.c_int),
+        ("v_keep", _ct.c_void_p), ("ld_vk", _ct.c_int),
+        ("freq", _ct.c_void_p), ("rot_dims", _ct.c_int), ("rot_mag", _ct.c_float), ("eps", _ct.c_float),
+        ("positions", _ct.c_void_p), ("seq_of_token", _ct.c_void_p), ("block_table", _ct.c_void_p),
+        ("max_pages", _ct.c_int), ("page_size", _ct.c_int), ("num_pages", _ct.c_int),
+        ("q_out", _ct.c_void_p), ("ldq", _ct.c_int), ("k_cache", _ct.c_void_p), ("v_cache", _ct.c_void_p),
+        ("q_head_stride", _ct.c_int), ("q_skip", _ct.c_int),
+    ]
+
+
+def head_prep(proj: torch.Tensor, ctx, block_table: torch.Tensor, page_size: int, *,
+              q_off: int, num_heads: int, q_dim: int, q_norm_w, q_norm_dims: int, q_rot_off: int,
+              k_off: int, num_kv_heads: int, k_dim: int, k_norm_w, k_norm_dims: int, k_rot_off: int,
+              v_off: int, v_dim: int, freq, rot_dims: int, rot_mag: float, eps: float,
+              q_out: torch.Tensor, k_cache, v_cache, lam=None, v_first=None, v_keep=None,
+              q_head_stride: Optional[int] = None, q_skip: int = 0) -> None:
+    """One launch between a mixer's first product and its attention: RMS norm of the first
+    ``*_norm_dims`` elements of every query / key head (weight shared by the heads; 0: none),
+    rotation of ``rot_dims`` elements from ``*_rot_off`` on (neighbouring pairs; ``freq`` float32
+    [rot_dims / 2]; cos and sin times ``rot_mag``), queries into ``q_out``, keys into the pages;
+    (head h at ``q_out[t, h * q_head_stride:]``, without its first ``q_skip`` elements);
+    values (``v_off`` < 0: none) mixed with ``v_first`` by ``lam`` (a float32 scalar on the
+    device) or copied to ``v_keep``, and into the pages.  A cache that is None is not written."""
+    a = _HeadPrepArgs()
+    a.proj, a.ld = proj.data_ptr(), proj.stride(0)
+    a.q_off, a.H, a.Dq, a.q_norm_dims, a.q_rot_off, a.q_norm_w = (q_off, num_heads, q_dim, q_norm_dims,
+                                                                  q_rot_off, _p(q_norm_w))
+    a.k_off, a.G, a.Dk, a.k_norm_dims, a.k_rot_off, a.k_norm_w = (k_off, num_kv_heads, k_dim, k_norm_dims,
+                                                                  k_rot_off, _p(k_norm_w))
+    a.v_off, a.Dv = v_off, (v_dim if v_off >= 0 else 0)
+    a.lam, a.v_first = _p(lam), _p(v_first)
+    a.ld_vf = v_first.stride(0) if v_first is not None else 0
+    a.v_keep = _p(v_keep)
+    a.ld_vk = v_keep.stride(0) if v_keep is not None else 0
+    a.freq, a.rot_dims, a.rot_mag, a.eps = _p(freq), rot_dims, float(rot_mag), float(eps)
+    a.positions, a.seq_of_token = ctx.positions.data_ptr(), ctx.seq_of_token.data_ptr()
+    a.block_table, a.max_pages, a.page_size = block_table.data_ptr(), block_table.shape[1], page_size
+    cache = k_cache if k_cache is not None else v_cache
+    a.num_pages = cache.shape[0] if cache is not None else 0
+    a.q_out, a.ldq = q_out.data_ptr(), q_out.stride(0)
+    a.k_cache, a.v_cache = _p(k_cache), _p(v_cache)
+    a.q_head_stride, a.q_skip = (q_dim if q_head_stride is None else q_head_stride), q_skip
+    fn = getattr(L.core(), "slb_head_prep_" + _suffix(proj.dtype))
+    L.check(fn(_ct.byref(a), proj.shape[0], _stream()), "head_prep")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x * sigmoid(gate), element by element ([T, N] views with any row stride)."""
+    fn = getattr(L.core(), "slb_sigmoid_gate_" + _suffix(x.dtype))
+    L.check(fn(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), out.data_ptr(), out.stride(0),
+               x.shape[0], x.shape[1], _stream()), "sigmoid_gate")
+
+
+def head_prep_status(reset: bool = False) -> int:
+    return L.core().slb_head_prep_status(1 if reset else 0)
+
+
+# ------------------------------------ attention with keys and values of two sizes
+def attention_kv_tile_rows() -> int:
+    return L.core().slb_attention_kv_tile_rows()
+
+
+def attention_kv_status(reset: bool = False) -> int:
+    return L.core().slb_attention_kv_status(1 if reset else 0)
+
+
+def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, num_heads: int,
+                 num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
+                 head_gate: Optional[torch.Tensor] = None) -> None:
+    """The plain kernel: float32 arithmetic; keys of ``k_dim``, values of ``v_dim`` elements at
+    ``v_cache`` with rows ``v_row_stride`` apart (the key cache itself for values that are a
+    prefix of the keys); ``head_gate`` [T, >= H]: head h's row times sigmoid(head_gate[t, h])."""
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, attention_kv_tile_rows())
+    fn = getattr(L.core(), "slb_attention_kv_" + _suffix(q.dtype))
+    L.check(fn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), v_row_stride,
+               out.data_ptr(), out.stride(0), block_table.data_ptr(), block_table.shape[1],
+               ctx.cu_q.data_ptr(), ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n,
+               num_heads, num_kv_heads, k_dim, v_dim, page_size, k_cache.shape[0], float(scale),
+               int(window), _p(head_gate), head_gate.stride(0) if head_gate is not None else 0,
+               _stream()), "attention_kv")
+
+
+# ----------------------------------------------------- per-head batches of products
+def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, b, :] = a[:, b, :] . w[b]^T for a [M, B, K], w [B, N, K], out [M, B, N] (views with
+    any row stride; the last dimension contiguous), on CUDA cores with float32 accumulation."""
+    M, B, Kd = a.shape
+    N = w.shape[1]
+    fn = getattr(L.core(), "slb_gemm_simt_batched_" + _suffix(a.dtype))
+    L.check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(1), out.data_ptr(), out.stride(0),
+               M, N, Kd, B, a.stride(1), w.stride(0), out.stride(1), _stream()), "gemm_simt_batched")
+
+
+def router_logits(x: torch.Tensor, w_f32: torch.Tensor) -> torch.Tensor:
+    """float32 logits x . w^T of a float32 router matrix (activations float32 or bfloat16)."""
+    M, Kd = x.shape
+    out = torch.empty((M, w_f32.shape[0]), dtype=_F32, device=x.device)
+    fn = L.core().slb_gemm_simt_f32 if x.dtype == _F32 else L.core().slb_gemm_simt_bf16_wf32
+    L.check(fn(x.data_ptr(), x.stride(0), w_f32.data_ptr(), w_f32.stride(0), out.data_ptr(), out.stride(0),
+               None, M, w_f32.shape[0], Kd, _stream()), "router_logits")
+    return out
+
+
+# ------------------------------------------------------------- routed experts
+def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, route_scale: float,
+              renormalize: bool):
+    """(ids int32 [T, top], weights float32 [T, top]) of the softmax router with group-limited
+    choice."""
+    T, E = logits.shape
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=_F32, device=logits.device)
+    L.check(L.core().slb_moe_route(logits.data_ptr(), logits.stride(0), T, E, groups, keep, top,
+                                   float(route_scale), 1 if renormalize else 0, ids.data_ptr(),
+                                   weights.data_ptr(), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, shared: Optional[torch.Tensor]) -> torch.Tensor:
+    """sum_k weights[t, k] * down_e(silu(gate_e x_t) * up_e x_t) (+ shared[t]), e = ids[t, k];
+    ``w_gate_up`` [E, 2 I, h] (gate rows, then up rows), ``w_down`` [E, h, I]."""
+    T, top = ids.shape
+    E, two_i, h = w_gate_up.shape
+    inter = two_i // 2
+    n_out = w_down.shape[1]
+    P = T * top
+    lib = L.core()
+    plan = torch.empty(lib.slb_moe_plan_ints(P, E), dtype=torch.int32, device=x.device)
+    L.check(lib.slb_moe_plan(ids.data_ptr(), P, E, plan.data_ptr(), _stream()), "moe_plan")
+    act = torch.empty((P, inter), dtype=x.dtype, device=x.device)
+    sfx = _suffix(x.dtype)
+    L.check(getattr(lib, "slb_moe_gate_up_" + sfx)(
+        x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), w_gate_up.stride(1), act.data_ptr(), act.stride(0),
+        plan.data_ptr(), E, P, top, inter, h, _stream()), "moe_gate_up")
+    y = torch.empty((P, n_out), dtype=_F32, device=x.device)
+    L.check(getattr(lib, "slb_moe_down_" + sfx)(
+        act.data_ptr(), act.stride(0), w_down.data_ptr(), w_down.stride(1), y.data_ptr(), y.stride(0),
+        plan.data_ptr(), E, P, top, n_out, inter, _stream()), "moe_down")
+    out = torch.empty((T, n_out), dtype=x.dtype, device=x.device)
+    L.check(getattr(lib, "slb_moe_combine_" + sfx)(
+        y.data_ptr(), y.stride(0), weights.data_ptr(), _p(shared),
+        shared.stride(0) if shared is not None else 0, out.data_ptr(), out.stride(0), T, top, n_out,
+        _stream()), "moe_combine")
+    return out

@@ -60,6 +60,30 @@ _CORE_SIGNATURES = {
     "slb_add_rmsnorm_parts_bf16": [P, P, I, LL, P, P, P, P, I, I, F, P],
     "slb_qkv_rope_cache_parts_bf16": [P, I, LL, I, P, P, P, P, I, I, I, P, I, P, I, P, P, I, I, I, I, P],
     "slb_gemm_tc_status": [I],
+    "slb_ln_add_norm_f32": [P, I, P, I, P, P, F, P, P, F, P, I, P, I, I, P],
+    "slb_ln_add_norm_bf16": [P, I, P, I, P, P, F, P, P, F, P, I, P, I, I, P],
+    "slb_head_prep_f32": [P, I, P],
+    "slb_head_prep_bf16": [P, I, P],
+    "slb_head_prep_status": [I],
+    "slb_sigmoid_gate_f32": [P, I, P, I, P, I, I, I, P],
+    "slb_sigmoid_gate_bf16": [P, I, P, I, P, I, I, I, P],
+    "slb_attention_kv_tile_rows": [],
+    "slb_attention_kv_status": [I],
+    "slb_attention_kv_f32": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
+    "slb_attention_kv_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
+    "slb_gemm_simt_batched_f32": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
+    "slb_gemm_simt_batched_bf16": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
+    "slb_gemm_simt_bf16_wf32": [P, I, P, I, P, I, P, I, I, I, P],
+    "slb_moe_tile_rows": [],
+    "slb_moe_route": [P, I, I, I, I, I, I, F, I, P, P, P],
+    "slb_moe_plan_ints": [I, I],
+    "slb_moe_plan": [P, I, I, P, P],
+    "slb_moe_gate_up_f32": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_gate_up_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_down_f32": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_down_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_combine_f32": [P, I, P, P, I, P, I, I, I, I, P],
+    "slb_moe_combine_bf16": [P, I, P, P, I, P, I, I, I, I, P],
 }
 
 # optional entry points: declared when the library exports them

@@ -196,3 +196,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         out = torch.mm(x, w.t())
     _mark("library gemm")
     return out
+
+
+def batched_head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, b, :] = a[:, b, :] . w[b]^T per head b: a [M, B, K], w [B, N, K], out [M, B, N]
+    (views; last dimension contiguous).  float32: this package's CUDA-core kernel (true 32-bit,
+    k-sequential sums); bfloat16: the vendor's batched product."""
+    if a.shape[0] == 0:
+        return
+    if a.dtype == torch.float32 or not use_vendor_batched:
+        K.gemm_simt_batched(a, w, out)
+        return
+    torch.bmm(a.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    _mark("library gemm")
+
+
+use_vendor_batched = False

@@ -116,3 +116,61 @@ class SandwichNormBlock(PreNormBlock):
         x = self.ff_norm.forward(ctx, resid, plain_unless(self.ff_norm, a))
         f = plain_unless(self.ff_post_norm, self.feed_forward.forward(ctx, plain_unless(self.feed_forward, x)))
         return resid, PostNormed(ctx, f, self.ff_post_norm)
+
+
+@register_block("result_norm")
+class ResultNormBlock(Block):
+    """x += norm1(mixer(x)); x += norm2(ff(x)): the sublayers read the stream itself and only
+    their results are normed.  A result travels as a ``PostNormed`` value to the kernel that adds
+    it, which also produces the next reader's copy of the stream (``LayerNorm.close``).
+    ``feed_forward`` None: the layer ends after the mixer."""
+    accepts_post_normed = True
+
+    @staticmethod
+    def _members(spec, prefix):
+        out = [(MIXERS, spec.mixer, f"{prefix}.{spec.mixer_name}"),
+               (NORMS, spec.mixer_post_norm, f"{prefix}.{spec.mixer_post_norm_name}")]
+        if spec.feed_forward is not None:
+            out += [(FEED_FORWARDS, spec.feed_forward, f"{prefix}.{spec.feed_forward_name}"),
+                    (NORMS, spec.ff_post_norm, f"{prefix}.{spec.ff_post_norm_name}")]
+        return tuple(out)
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and spec.ff_post_norm is None):
+            raise ValueError("result_norm: every sublayer needs a norm on its result")
+        self._parts = [build_part(t, part, name, env) for t, part, name in self._members(spec, prefix)]
+        self.mixer, self.mixer_post_norm = self._parts[:2]
+        self.feed_forward, self.ff_post_norm = self._parts[2:] if len(self._parts) > 2 else (None, None)
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self._parts)
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        out = []
+        for table, part, name in cls._members(spec, prefix):
+            out += part_class(table, part).declare(part, name)
+        return out
+
+    @classmethod
+    def cache_request(cls, spec):
+        return part_class(MIXERS, spec.mixer).cache_request(spec.mixer)
+
+    def load(self, store):
+        for p in self._parts:
+            p.load(store)
+
+    def forward(self, ctx, resid, delta, cache, owns_cache):
+        from .norm import LayerNorm
+        h = LayerNorm.close(ctx, resid, delta, self.env.dtype)
+        a = K_plain(self.mixer.forward(ctx, h, cache, owns_cache))
+        a = PostNormed(ctx, a, self.mixer_post_norm)
+        if self.feed_forward is None:
+            return resid, a
+        h = LayerNorm.close(ctx, resid, a, self.env.dtype)
+        f = K_plain(self.feed_forward.forward(ctx, h))
+        return resid, PostNormed(ctx, f, self.ff_post_norm)
+
+
+def K_plain(value):
+    """A part's result as a plain tensor (unfinished forms are finished)."""
+    return plain_unless(None, value)

@@ -116,3 +116,68 @@ class DynamicTanh(Norm):
     def add_into(self, ctx, resid, delta) -> None:
         """resid += this norm of ``delta`` (the close of a branch that nothing norms after)."""
         K.dyt_add_norm(resid, delta, self.params, None, None, None)
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * w + b in float32.  As the pending norm of a ``PostNormed``
+    update it runs inside the kernel that adds the update to the stream (``close``), which also
+    hands the stream to the next reader in the compute dtype."""
+    graph_safe = True
+    accepts_post_normed = True
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        return [TensorDecl(prefix + spec.weight_suffix, (spec.dim,), NORM),
+                TensorDecl(prefix + spec.bias_suffix, (spec.dim,), BIAS)]
+
+    def load(self, store):
+        self.weight = store.get(self.prefix + self.spec.weight_suffix)
+        self.bias = store.get(self.prefix + self.spec.bias_suffix)
+        self.params = (self.weight, self.bias, self.spec.eps)
+
+    @staticmethod
+    def _pending(delta):
+        """(update tensor or None, its pending layer norm's parameters or None)."""
+        if isinstance(delta, PostNormed):
+            if isinstance(delta.norm, LayerNorm):
+                return K.plain_unless(None, delta.value), delta.norm.params
+            return delta.materialize(), None
+        return (None if delta is None else K.plain_unless(None, delta)), None
+
+    def forward(self, ctx, resid, delta, out_rows=None):
+        """The norm of the stream's rows (after the update) -- the use as a model's final norm."""
+        delta, post = self._pending(delta)
+        if delta is not None and post is None:
+            if out_rows is not None:                  # a plain update and selected rows: add first
+                resid = resid + delta.to(torch.float32)
+            else:
+                resid += delta.to(torch.float32)
+            delta = None
+        rows = resid.shape[0] if out_rows is None else out_rows.numel()
+        out = torch.empty((rows, self.spec.dim), dtype=self.env.dtype, device=resid.device)
+        K.ln_add_norm(resid, delta, post, self.params, out, out_rows)
+        return out
+
+    def apply(self, ctx, x):
+        stream = x.to(torch.float32)
+        out = torch.empty((x.shape[0], self.spec.dim), dtype=self.env.dtype, device=x.device)
+        K.ln_add_norm(stream, None, None, self.params, out, None)
+        return out
+
+    @classmethod
+    def close(cls, ctx, resid, delta, dtype):
+        """Adds a pending update into the float32 stream (its layer norm applied on the way) and
+        returns the stream for the next reader: the stream itself in float32, else a copy in
+        ``dtype``.  One launch."""
+        delta, post = cls._pending(delta)
+        if delta is not None and post is None:
+            resid += delta.to(torch.float32)
+            delta = None
+        if dtype == torch.float32:
+            if delta is not None:
+                K.ln_add_norm(resid, delta, post, None, None, None)
+            return resid
+        out = torch.empty(resid.shape, dtype=dtype, device=resid.device)
+        K.ln_add_norm(resid, delta, post, None, out, None)
+        return out

@@ -9,6 +9,8 @@ its table.  ``none``: no position information.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding
@@ -30,6 +32,39 @@ class RotaryEmbedding(PositionEncoding):
 
     def rotary_table(self):
         return self.inv_freq, self.rotary_dim
+
+
+@register_position("rotary_pairs")
+class PairRotary(PositionEncoding):
+    """Rotation of neighbouring pairs (2i, 2i + 1), optionally with YaRN-scaled frequencies.
+    ``pair_table()`` -> (frequencies float32 [dims / 2], dims, factor on cos and sin); the
+    rotation itself runs in the mixer's head kernel (``ops.kernels.head_prep``).  The
+    frequencies are formed in float64 on the host and rounded once."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix, env):
+        super().__init__(spec, prefix, env)
+        d = spec.dims
+        if d <= 0 or d % 2:
+            raise ValueError(f"rotary_pairs: dims must be positive and even, got {d}")
+        i = torch.arange(d // 2, dtype=torch.float64)
+        f = float(spec.theta) ** (-2.0 * i / d)
+        self.magnitude = 1.0
+        if spec.yarn_factor is not None:
+            factor = float(spec.yarn_factor)
+
+            def pair_that_turns(times: float) -> float:
+                return d * math.log(spec.yarn_original / (2.0 * math.pi * times)) / (2.0 * math.log(spec.theta))
+            lo = max(math.floor(pair_that_turns(spec.yarn_fast)), 0)
+            hi = min(math.ceil(pair_that_turns(spec.yarn_slow)), d - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(factor) + 1.0
+        self.dims = d
+        self.freq = f.to(torch.float32).to(env.device)
+
+    def pair_table(self):
+        return self.freq, self.dims, self.magnitude
 
 
 @register_position("none")
