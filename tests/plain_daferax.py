@@ -185,3 +185,33 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], streams: O
             streams.append(x.clone())
     x = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
     return x @ W["embed"].T
+
+
+def greedy(cfg, W, prompt: List[int], steps: int) -> List[int]:
+    ids = list(prompt)
+    for _ in range(steps):
+        ids.append(int(torch.argmax(forward(cfg, W, ids)[-1])))
+    return ids[len(prompt):]
+
+
+def load_folder(folder: str):
+    """(config dict, name -> float64 tensor) of a model folder; reads the safetensors file
+    itself: 8 bytes of header length, the JSON header, then the data."""
+    import json
+    import os
+    import struct
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+        raw = f.read()
+    n = struct.unpack("<Q", raw[:8])[0]
+    header = json.loads(raw[8:8 + n])
+    kinds = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16, "I32": torch.int32}
+    out = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = meta["data_offsets"]
+        t = torch.frombuffer(bytearray(raw[8 + n + a:8 + n + b]), dtype=kinds[meta["dtype"]])
+        out[name] = t.to(F64).reshape(meta["shape"])
+    return cfg, out

@@ -1,0 +1,458 @@
+"""Daferax on the GPU against the plain implementation (``plain_daferax``): every new kernel
+alone, then whole models replayed whole, token by token, in portions down to two tokens and in
+mixed batches with pages and slots used again, in float32 and bfloat16, and greedy generation
+through the engine."""
+
+import numpy as np
+import pytest
+import torch
+
+import daferax_cases as C
+import helpers as H
+import plain_daferax as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+F64 = torch.float64
+
+
+def _ctx(entries, groups=1):
+    from servelab_b200.engine.batch import StepContext
+    return StepContext.pack(entries, groups, DEV)
+
+
+def _entry(tokens, start, table):
+    from servelab_b200.engine.batch import BatchEntry
+    return BatchEntry(tokens=[0] * tokens, start=start, want=(), block_tables=[table], state_slot=0)
+
+
+# ------------------------------------------------------------------ norm
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [48, 77, 1024])
+def test_layer_norm_kernel(dtype, dim):
+    from servelab_b200.ops import kernels as K
+    g = torch.Generator().manual_seed(dim)
+    T = 9
+    resid = torch.randn(T, dim, generator=g) * 2
+    delta = (torch.randn(T, dim, generator=g) * 3 + 5).to(dtype)          # (a mean far from zero)
+    post = (torch.randn(dim, generator=g), torch.randn(dim, generator=g), 1e-5)
+    pre = (torch.randn(dim, generator=g), torch.randn(dim, generator=g), 1e-3)
+    dev = lambda p: (p[0].to(DEV), p[1].to(DEV), p[2])
+    want_resid = resid.double() + plain.layer_norm(delta.double(), post[0].double(), post[1].double(), 1e-5)
+    want_out = plain.layer_norm(want_resid, pre[0].double(), pre[1].double(), 1e-3)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    r = resid.to(DEV)
+    out = torch.empty(T, dim, dtype=dtype, device=DEV)
+    K.ln_add_norm(r, delta.to(DEV), dev(post), dev(pre), out)
+    assert (r.cpu().double() - want_resid).abs().max() < 1e-5              # the stream stays float32
+    assert (out.cpu().double() - want_out).abs().max() < tol
+    # rows selected: the stream is left alone, the update still counts for the selected rows
+    rows = torch.tensor([7, 2], dtype=torch.int32, device=DEV)
+    r2 = resid.to(DEV)
+    out2 = torch.empty(2, dim, dtype=dtype, device=DEV)
+    K.ln_add_norm(r2, delta.to(DEV), dev(post), dev(pre), out2, rows)
+    assert torch.equal(r2.cpu(), resid) and torch.equal(out2, out[[7, 2]])
+    # the add alone with a copy of the stream for the next reader; a copy without an update
+    r3 = resid.to(DEV)
+    copy = torch.empty(T, dim, dtype=dtype, device=DEV)
+    K.ln_add_norm(r3, delta.to(DEV), dev(post), None, copy)
+    assert torch.equal(r3, r) and (copy.cpu().double() - want_resid).abs().max() < tol
+    K.ln_add_norm(r3, None, None, None, copy)
+    assert torch.equal(copy, r3.to(dtype))
+
+
+# ------------------------------------------- head norms, rotation, value mix
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8, 8), (3, 3, 10, 6, 4), (2, 1, 64, 96, 64)])
+def test_head_kernel_norms_rotates_mixes_and_writes_the_pages(dtype, shape):
+    """Two requests at different positions in one step: q against the oracle's normed, rotated
+    heads; keys and mixed values where the block tables say."""
+    from servelab_b200.ops import kernels as K
+    Hq, G, D, Dv, rd = shape
+    ps, pages = 4, 40
+    g = torch.Generator().manual_seed(D)
+    starts, lens = [37, 0], [6, 3]
+    T = sum(lens)
+    width = Hq * D + G * D + G * Dv + 5
+    proj = torch.randn(T, width, generator=g).to(dtype)
+    qw, kw = torch.randn(D, generator=g), torch.randn(D, generator=g)
+    vf = torch.randn(T, G * Dv, generator=g).to(dtype)
+    lam = torch.tensor([0.3])
+    order = torch.randperm(pages, generator=g).tolist()
+    tables = [order[:12], order[12:14]]
+    ctx = _ctx([_entry(n, s, t) for n, s, t in zip(lens, starts, tables)])
+    scaling = {"factor": 3.0, "original": 16, "fast": 4.0, "slow": 1.0}
+    f, mag = plain.rotary_frequencies(rd, 777.0, scaling)
+    kc = torch.zeros(pages, G, ps, D, dtype=dtype, device=DEV)
+    vc = torch.zeros(pages, G, ps, Dv, dtype=dtype, device=DEV)
+    q = torch.empty(T, Hq * D, dtype=dtype, device=DEV)
+    keep = torch.empty(T, G * Dv, dtype=dtype, device=DEV)
+    K.head_prep(proj.to(DEV), ctx, ctx.block_tables[0], ps, q_off=0, num_heads=Hq, q_dim=D,
+                q_norm_w=qw.to(DEV), q_norm_dims=D, q_rot_off=0, k_off=Hq * D, num_kv_heads=G, k_dim=D,
+                k_norm_w=kw.to(DEV), k_norm_dims=D, k_rot_off=0, v_off=Hq * D + G * D, v_dim=Dv,
+                freq=f.float().to(DEV), rot_dims=rd, rot_mag=mag, eps=1e-5, q_out=q, k_cache=kc, v_cache=vc,
+                lam=lam.to(DEV), v_first=vf.to(DEV), v_keep=keep)
+    assert K.head_prep_status() == 0
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)])
+    p64 = proj.double()
+    want_q = plain.rotate_pairs(plain.rms_norm(p64[:, :Hq * D].view(T, Hq, D), qw.double(), 1e-5), pos, rd, 777.0, scaling)
+    want_k = plain.rotate_pairs(plain.rms_norm(p64[:, Hq * D:Hq * D + G * D].view(T, G, D), kw.double(), 1e-5),
+                                pos, rd, 777.0, scaling)
+    v_raw = p64[:, Hq * D + G * D:Hq * D + G * D + G * Dv]
+    want_v = (0.7 * v_raw + 0.3 * vf.double()).view(T, G, Dv)
+    tol = 2e-5 if dtype == torch.float32 else 4e-2
+    assert (q.cpu().double().view(T, Hq, D) - want_q).abs().max() < tol
+    assert (keep.cpu().double() - v_raw).abs().max() < tol
+    t = 0
+    for s, n, table in zip(starts, lens, tables):
+        for p in range(s, s + n):
+            page, slot = table[p // ps], p % ps
+            assert (kc[page, :, slot].cpu().double() - want_k[t]).abs().max() < tol
+            assert (vc[page, :, slot].cpu().double() - want_v[t]).abs().max() < tol
+            t += 1
+    written = sum(lens) * G * D
+    assert int((kc != 0).sum()) <= written                  # nothing beyond the tokens' slots
+
+
+# ---------------------------------------------------------------- attention
+def _attention_case(seed, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, spike=None):
+    """Requests with contexts ``ctxs`` whose last ``qlens`` tokens are this step's queries; keys
+    and values in pages in a shuffled order.  ``spike`` = distance: the key at that distance
+    from every query's position gets a score far above the others and a value of its own."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-c // ps) for c in ctxs) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    row = Dk if tied else Dv
+    kc = torch.full((n_pages, G, ps, Dk), 1e30, dtype=dtype)
+    vc = kc if tied else torch.full((n_pages, G, ps, Dv), 1e30, dtype=dtype)
+    qs, wants, entries = [], [], []
+    for c, n in zip(ctxs, qlens):
+        k = torch.randn(c, G, Dk, generator=g) * 0.5
+        v = k[..., :Dv].clone() if tied else torch.randn(c, G, Dv, generator=g)
+        q = torch.randn(n, Hq, Dk, generator=g) * 0.5
+        if spike is not None:
+            for i in range(n):
+                j = c - n + i - spike
+                if j >= 0:
+                    if tied:                       # only the part of the key that is no value
+                        k[j, :, Dv:] = 3.0
+                        q[i, :, Dv:] = 3.0
+                    else:
+                        k[j] = 1.5
+                        q[i] = 1.5
+                        v[j] = 7.0
+        k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+        table = [order.pop() for _ in range(-(-c // ps))]
+        for p in range(c):
+            kc[table[p // ps], :, p % ps] = k[p]
+            if not tied:
+                vc[table[p // ps], :, p % ps] = v[p]
+        rep = Hq // G
+        kk, vv = k.double().repeat_interleave(rep, 1), v.double().repeat_interleave(rep, 1)
+        s = torch.einsum("ihd,jhd->hij", q.double(), kk) * 0.2
+        i = torch.arange(c - n, c)[:, None]
+        j = torch.arange(c)[None, :]
+        ok = (j <= i) & ((i - j < window) if window else True)
+        s = s.masked_fill(~ok[None], float("-inf"))
+        wants.append(torch.einsum("hij,jhd->ihd", torch.softmax(s, -1), vv).reshape(n, Hq * Dv))
+        qs.append(q.reshape(n, Hq * Dk))
+        entries.append(_entry(n, c - n, table))
+    return {"q": torch.cat(qs).to(DEV), "kc": kc.to(DEV), "vc": kc.to(DEV) if tied else vc.to(DEV),
+            "want": torch.cat(wants), "entries": entries, "row": row}
+
+
+SHAPES = [(4, 2, 48, 32, None), (8, 1, 160, 128, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("spike", ["in", "out", "far", None])
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_with_keys_and_values_of_two_sizes(dtype, spike, shape, decode):
+    """Portions and single tokens at page and window edges; a key made dominant just inside the
+    window, just outside it (it must not count), or hundreds of tokens back."""
+    from servelab_b200.ops import attention as A
+    Hq, G, Dk, Dv, window = shape
+    tied = G == 1 and Dv < Dk
+    dist = {"in": (window or 300) - 1, "out": window or 0, "far": 290, None: None}[spike]
+    if spike == "out" and not window:
+        pytest.skip("no window: nothing is outside")
+    if spike == "far" and window and window <= 290:
+        dist = window - 1
+    ps = 8
+    ctxs = [1, 2, 300, 301, 64, 65, 333] + ([window, window + 1] if window else [])
+    qlens = [1] * len(ctxs) if decode else [1, 2, 200, 37, 64, 3, 33] + ([window, 2] if window else [])
+    case = _attention_case(7, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, dist)
+    ctx = _ctx(case["entries"])
+    out = torch.empty(case["q"].shape[0], Hq * Dv, dtype=dtype, device=DEV)
+    A.kv_attention(ctx, case["q"], case["kc"], case["vc"], case["row"], out, ctx.block_tables[0], Hq, G, Dk, Dv,
+                   ps, 0.2, window or 0, None)
+    got = out.cpu().double()
+    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    assert (got - case["want"]).abs().max() < tol * max(1.0, float(case["want"].abs().max()))
+    if dtype == torch.bfloat16:
+        A.force_generic = True                    # the plain kernel, the twin of the fast ones
+        try:
+            twin = torch.empty_like(out)
+            A.kv_attention(ctx, case["q"], case["kc"], case["vc"], case["row"], twin, ctx.block_tables[0], Hq, G,
+                           Dk, Dv, ps, 0.2, window or 0, None)
+        finally:
+            A.force_generic = False
+        assert (twin.cpu().double() - case["want"]).abs().max() < tol * max(1.0, float(case["want"].abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_gate_per_head(dtype):
+    from servelab_b200.ops import attention as A
+    Hq, G, Dk, Dv = 4, 2, 16, 8
+    case = _attention_case(3, Hq, G, Dk, Dv, None, [40, 9], [5, 1], 8, dtype, False)
+    ctx = _ctx(case["entries"])
+    gate = torch.randn(6, Hq + 3, generator=torch.Generator().manual_seed(1)).to(dtype).to(DEV)
+    out = torch.empty(6, Hq * Dv, dtype=dtype, device=DEV)
+    A.kv_attention(ctx, case["q"], case["kc"], case["vc"], Dv, out, ctx.block_tables[0], Hq, G, Dk, Dv, 8, 0.2, 0,
+                   gate)
+    want = case["want"].view(6, Hq, Dv) * torch.sigmoid(gate.cpu().double()[:, :Hq, None])
+    assert (out.cpu().double().view(6, Hq, Dv) - want).abs().max() < (1e-5 if dtype == torch.float32 else 4e-2)
+
+
+# ------------------------------------------------------------------ experts
+@pytest.mark.parametrize("shape", [(6, 3, 2, 2), (8, 1, 1, 1), (64, 8, 4, 6), (12, 3, 2, 3), (5, 1, 1, 5)])
+def test_router_kernel(shape):
+    from servelab_b200.ops import kernels as K
+    E, groups, keep, top = shape
+    T = 50
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(E)) * 2
+    r = {"experts": E, "top": top, "scale": 2.5}
+    if groups > 1:
+        r["groups"] = {"count": groups, "keep": keep}
+    want_idx, want_w = plain.route(logits.double(), {"x.router": torch.eye(E, dtype=F64)}, "x.", r)
+    ids, w = K.moe_route(logits.to(DEV), groups, keep, top, 2.5, False)
+    assert torch.equal(ids.cpu().long(), want_idx)
+    assert (w.cpu().double() - want_w).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [1, 7, 150])
+def test_experts_kernels(dtype, T):
+    """The planned products and the weighted sum against the oracle, with experts that get no
+    token and experts that get more than a tile."""
+    from servelab_b200.ops import kernels as K
+    E, top, h, inter = 7, 3, 40, 24
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, h, generator=g).to(dtype)
+    Wm = {f"m.e{j}.{n}": (torch.randn(s, generator=g) * 0.2).to(dtype).double()
+          for j in range(E) for n, s in (("gate", (inter, h)), ("up", (inter, h)), ("down", (h, inter)))}
+    ids = torch.stack([torch.randperm(E - 2, generator=g)[:top] for _ in range(T)]).int()    # experts 5, 6 idle
+    wgt = torch.rand(T, top, generator=g)
+    shared = torch.randn(T, h, generator=g).to(dtype)
+    want = shared.double().clone()
+    for t in range(T):
+        for e, c in zip(ids[t].tolist(), wgt[t].double()):
+            want[t] += c * plain.gated_ff(x[t:t + 1].double(), Wm, f"m.e{e}.")[0]
+    w_gu = torch.stack([torch.cat([Wm[f"m.e{j}.gate"], Wm[f"m.e{j}.up"]]) for j in range(E)]).to(dtype).to(DEV)
+    w_dn = torch.stack([Wm[f"m.e{j}.down"] for j in range(E)]).to(dtype).to(DEV)
+    out = K.moe_experts(x.to(DEV), ids.to(DEV), wgt.to(DEV), w_gu, w_dn, shared.to(DEV))
+    assert (out.cpu().double() - want).abs().max() < (1e-4 if dtype == torch.float32 else 6e-2)
+
+
+# ------------------------------------------------------------ whole models
+LENGTHS = [70, 45, 190, 33, 2, 1, 58]
+TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+@pytest.fixture(scope="module", params=["U", "V", "W"])
+def model(request, tmp_path_factory):
+    cfg, seed, page = C.CASES[request.param]
+    folder = C.make_model(str(tmp_path_factory.mktemp(f"daf_{request.param}")), cfg, seed)
+    reqs = {f"r{i}": H.random_ids(n, cfg["vocab"], 100 * seed + i) for i, n in enumerate(LENGTHS)}
+    pc, pw = plain.load_folder(folder)
+    ref = {rid: plain.forward(pc, pw, ids).float().numpy() for rid, ids in reqs.items()}
+    return {"name": request.param, "cfg": cfg, "folder": folder, "page": page, "requests": reqs,
+            "ref": ref, "plain": (pc, pw)}
+
+
+def _bulk_tail(requests, tail):
+    steps = H.trace_bulk_tail(requests, tail=tail)
+    last = {}
+    for st in steps:
+        for e in st["entries"]:
+            last[e["id"]] = st
+    for rid, st in last.items():
+        if rid not in st["end"]:
+            st["end"].append(rid)
+    return steps
+
+
+def _replay(model, dtype, steps, max_tokens=None, **kw):
+    from servelab_b200.replay import TraceSession
+    sess = TraceSession(model["folder"], dtype, max_tokens or H.peak_tokens(steps), page_size=model["page"],
+                        max_live=4, poison_cache=True, **kw)
+    got = H.collect(steps, H.run_session(sess, steps), model["cfg"]["vocab"])
+    sess.cache.check_invariants()
+    assert not sess.held and all(p.num_free() == p.num_pages for p in sess.cache.pools)
+    assert sess.cache.slots.num_free() == 4
+    return got, sess
+
+
+def _compare(model, dtype, got):
+    scale = max(float(np.abs(r).max()) for r in model["ref"].values())
+    worst = 0.0
+    for rid, ids in model["requests"].items():
+        assert sorted(got[rid]) == list(range(len(ids))), f"{rid}: positions missing"
+        for pos in range(len(ids)):
+            err = float(np.abs(got[rid][pos] - model["ref"][rid][pos]).max())
+            assert err <= TOL[dtype] * max(1.0, scale), (
+                f"config {model['name']} {dtype} request {rid}: first wrong position {pos} (err {err:.3e})")
+            worst = max(worst, err)
+    print(f"config {model['name']} {dtype}: worst abs logit error {worst:.3e} (logits up to {scale:.2f})")
+
+
+def test_the_residual_stream_after_every_layer(model):
+    from servelab_b200.parts.norm import LayerNorm
+    from servelab_b200.replay import TraceSession
+    pc, pw = model["plain"]
+    streams = []
+    ids = model["requests"]["r1"]
+    plain.forward(pc, pw, ids, streams)
+    sess = TraceSession(model["folder"], "float32", 64, page_size=model["page"])
+    seen = []
+    for block in sess.runner.model.blocks:
+        def fwd(ctx, resid, delta, cache, owns, _f=block.forward):
+            resid, delta = _f(ctx, resid, delta, cache, owns)
+            closed = resid.clone()
+            LayerNorm.close(ctx, closed, delta, torch.float32)
+            seen.append(closed.double().cpu())
+            return resid, delta
+        block.forward = fwd
+    sess.run_step({"step": 0, "entries": [{"id": "x", "tokens": ids, "want": []}], "end": ["x"]})
+    assert len(seen) == len(streams)
+    for i, (got, want) in enumerate(zip(seen, streams)):
+        assert (got - want).abs().max() < 1e-4 * max(1.0, float(want.abs().max())), f"layer {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole(model, dtype):
+    got, _ = _replay(model, dtype, H.trace_whole(model["requests"]))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_then_token_by_token_beyond_every_window(model, dtype):
+    """The last 120 tokens one by one: every window passes over decoded tokens, and windowed
+    groups give pages back while the request still decodes."""
+    got, _ = _replay(model, dtype, _bulk_tail(model["requests"], 120))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_down_to_two_tokens(model, dtype):
+    got, _ = _replay(model, dtype, H.trace_portions(model["requests"]))
+    _compare(model, dtype, got)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_with_pages_and_slots_used_again(model, dtype):
+    steps = H.trace_mixed(model["requests"], seed=4)
+    need = H.peak_tokens(steps)
+    assert need < sum(-(-len(v) // 64) * 64 for v in model["requests"].values())
+    assert len(model["requests"]) > 4                       # more requests than slots
+    got, _ = _replay(model, dtype, steps, need)
+    _compare(model, dtype, got)
+
+
+def test_float32_logits_do_not_depend_on_the_cut(model):
+    whole, _ = _replay(model, "float32", H.trace_whole(model["requests"]))
+    for steps in (H.trace_portions(model["requests"]), H.trace_mixed(model["requests"], seed=9),
+                  _bulk_tail(model["requests"], 40)):
+        got, _ = _replay(model, "float32", steps)
+        for rid in whole:
+            for pos in whole[rid]:
+                assert np.abs(got[rid][pos] - whole[rid][pos]).max() <= 2e-6, (rid, pos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_single_token_steps_through_replayed_graphs(model, dtype):
+    steps = _bulk_tail(model["requests"], 40)
+    eager, _ = _replay(model, dtype, steps)
+    graphs, sess = _replay(model, dtype, steps, cuda_graphs=True)
+    assert sess.runner.graph_replays > 0
+    for rid in eager:
+        for pos in eager[rid]:
+            assert np.abs(graphs[rid][pos] - eager[rid][pos]).max() <= (2e-6 if dtype == "float32" else 2e-1)
+    _compare(model, dtype, graphs)
+
+
+def test_the_trace_runner_as_a_program(model, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = H.trace_mixed(model["requests"], seed=21)
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model["folder"], "--dtype", "bfloat16",
+         "--out", str(out), "--max-tokens", str(H.peak_tokens(steps)), "--page-size", str(model["page"])],
+        input="".join(json.dumps(st) + "\n" for st in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")] == [f"done {st['step']}" for st in steps]
+    V = model["cfg"]["vocab"]
+    outputs = {st["step"]: np.fromfile(out / f"{st['step']}.f32", dtype="<f4").reshape(-1, V)
+               for st in steps if any(e["want"] for e in st["entries"])}
+    _compare(model, "bfloat16", H.collect(steps, outputs, V))
+
+
+# --------------------------------------------------------------- generation
+def _engine(model, dtype="float32", num_blocks=256, budget=2048, **kw):
+    from servelab_b200.config import CacheConfig, SchedulerConfig
+    from servelab_b200.engine.llm_engine import LLMEngine
+    return LLMEngine(model["folder"], CacheConfig(block_size=model["page"], num_blocks=num_blocks),
+                     SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=budget), dtype=dtype, **kw)
+
+
+def test_greedy_generation_through_the_engine(model):
+    """The entry point and its scheduler (continuous batching, portions under a token budget,
+    graphs, look-ahead) generate what the oracle generates, also with so few pages that requests
+    are preempted and recomputed."""
+    from servelab_b200.sampling import SamplingParams
+    pc, pw = model["plain"]
+    prompts = [model["requests"][r][:n] for r, n in (("r0", 41), ("r1", 3), ("r2", 77), ("r5", 1), ("r3", 20))]
+    n_new = 14
+    want = [plain.greedy(pc, pw, p, n_new) for p in prompts]
+    sp = SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True)
+    outs = _engine(model).generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    outs = _engine(model, budget=16, cuda_graphs=False).generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    few = -(-(77 + n_new) // model["page"]) + 2
+    eng = _engine(model, num_blocks=few, budget=24)
+    outs = eng.generate(prompts, sp)
+    assert [o.outputs[0].token_ids for o in outs] == want
+    eng.runner.cache.check_invariants()
+    st = eng.stats()
+    assert st["running"] == 0 and st["pages_used"] == [0] * len(st["pages_used"])
+
+
+def test_command_line(model, tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+    if model["name"] != "U":
+        pytest.skip("one configuration is enough for the command line")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pc, pw = model["plain"]
+    want = plain.greedy(pc, pw, [3, 1, 4, 1, 5], 6)
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--model", model["folder"],
+                        "--prompt-ids", "3,1,4,1,5", "--max-tokens", "6", "--temperature", "0",
+                        "--dtype", "float32", "--ignore-eos", "--block-size", "8", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert f"finish=length -> {want}" in r.stdout and "stats:" in r.stdout
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(C.W))
+    r = subprocess.run([sys.executable, "-m", "servelab_b200", "--random-weights", str(cfg_path),
+                        "--prompt-ids", "1,2,3", "--max-tokens", "5", "--temperature", "0.8", "--seed", "3",
+                        "--ignore-eos", "--block-size", "4", "--num-blocks", "32"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "finish=length" in r.stdout, r.stderr[-2000:]
