@@ -43,6 +43,111 @@ def qwen2_config(width, heads, kv, dim, ff, layers=LAYERS) -> dict:
                 max_window_layers=0)
 
 
+# Daferax: layers alternate between the latent attention (windowed) and the grouped-query
+# attention (every earlier key), each followed by routed experts with a shared expert.  The Qwen2
+# model beside it has the same width, heads, kv heads, head size and layer count, a dense
+# feed-forward of the size a Daferax token ACTIVATES (top experts + shared), and its upper half of
+# layers windowed.  width, heads, kv heads, head size (keys = values), latent size, rotated part,
+# experts, groups, kept groups, top, expert size, shared size
+DAFERAX_SIZES = {
+    "lite-2048": (2048, 16, 4, 128, 256, 64, 32, 4, 2, 4, 1408, 2816),
+    "small-1024": (1024, 8, 2, 64, 128, 32, 16, 2, 1, 2, 512, 1024),
+}
+
+
+def daferax_config(width, heads, kv, dim, rank, rot, experts, groups, keep, top, eff, sff, layers=LAYERS) -> dict:
+    mlp = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
+           "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "scale": 2.5, "top": top}}
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
+              "scale": (dim + rot) ** -0.5, "mask": {"size": WINDOW},
+              "rot": {"base": 500000.0, "dims": rot,
+                      "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+            "rot": {"base": 1000000.0, "dims": dim}}
+    return {"architecture": "Daferax", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention" if i % 2 == 0 else "attention",
+                        "mixer": latent if i % 2 == 0 else attn, "mlp": mlp} for i in range(layers)]}
+
+
+def qwen2_like_daferax(width, heads, kv, dim, rank, rot, experts, groups, keep, top, eff, sff, layers=LAYERS) -> dict:
+    cfg = qwen2_config(width, heads, kv, dim, top * eff + sff, layers)
+    cfg["max_window_layers"] = layers // 2            # the upper half of the layers is windowed
+    return cfg
+
+
+def _daferax_rooflines(size, res, peaks) -> Dict[str, object]:
+    """Microseconds per launch and achieved fractions of the measured peaks for the kernels of the
+    Daferax layers beside their Qwen2 counterparts, from the eager profiles.  Prefill attention:
+    flops of the visible (query, key) pairs, 2 (Dk + Dv) per pair and head, of the bf16 peak -- for
+    the latent attention Dk and Dv are what the absorbed form multiplies (latent + rotated part,
+    latent).  Decode attention: bytes of the cached rows the 8 requests may see, of the copy
+    bandwidth.  Elementwise kernels: bytes they must move, of the copy bandwidth.  Experts
+    (prefill): 6 tokens top width expert_size flops of the bf16 peak; (decode, 8 tokens): bytes of
+    the weights of the experts that at most 8 top pairs can touch."""
+    width, heads, kv, dim, rank, rot, experts, groups, keep, top, eff, sff = DAFERAX_SIZES[size]
+    out: Dict[str, object] = {}
+    pk, dk = res["daferax"]["prefill_kernels_us"], res["daferax"]["decode_b8_kernels_us"]
+    qk, qd = res["qwen2"]["prefill_kernels_us"], res["qwen2"]["decode_b8_kernels_us"]
+    n_lat, n_att = (LAYERS + 1) // 2, LAYERS // 2
+    full_pairs = PROMPT * (PROMPT + 1) / 2
+    win_pairs = sum(min(t + 1, WINDOW) for t in range(PROMPT))
+
+    def hbm(nbytes, us):
+        return round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4)
+
+    def tf(flops, us):
+        return round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
+
+    att = pk.get("attention_kv_mma") or pk.get("attention_kv")
+    if att:
+        flops = (n_lat * win_pairs * heads * 2 * (2 * rank + rot) + n_att * full_pairs * heads * 2 * 2 * dim)
+        out["daferax_prefill_attention_us_per_layer"] = round(att / LAYERS, 1)
+        out["daferax_prefill_attention_bf16_frac"] = tf(flops, att)
+    qatt = (qk.get("prefill_attention_tc") or 0) + (qk.get("prefill_attention") or 0)
+    if qatt:
+        flops = (LAYERS // 2 * win_pairs + (LAYERS - LAYERS // 2) * full_pairs) * heads * 4 * dim
+        out["qwen2_prefill_attention_us_per_layer"] = round(qatt / LAYERS, 1)
+        out["qwen2_prefill_attention_bf16_frac"] = tf(flops, qatt)
+    datt = dk.get("attention_kv_mma") or dk.get("attention_kv")
+    if datt:
+        nbytes = 8 * 2 * (n_lat * min(CONTEXT, WINDOW) * (rank + rot) + n_att * CONTEXT * kv * 2 * dim)
+        out["daferax_decode_attention_us_per_layer"] = round(datt / LAYERS, 2)
+        out["daferax_decode_attention_hbm_frac"] = hbm(nbytes, datt)
+    qdatt = qd.get("decode_attention")
+    if qdatt:
+        nbytes = 8 * 2 * kv * 2 * dim * (LAYERS // 2 * min(CONTEXT, WINDOW) + (LAYERS - LAYERS // 2) * CONTEXT)
+        out["qwen2_decode_attention_us_per_layer"] = round(qdatt / LAYERS, 2)
+        out["qwen2_decode_attention_hbm_frac"] = hbm(nbytes, qdatt)
+    if pk.get("ln_add_norm"):
+        us = pk["ln_add_norm"] / (2 * LAYERS + 1)
+        out["daferax_norm_us"], out["daferax_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if qk.get("add_rmsnorm"):
+        us = qk["add_rmsnorm"] / (2 * LAYERS + 1)
+        out["qwen2_norm_us"], out["qwen2_norm_hbm_frac"] = round(us, 2), hbm(PROMPT * 12 * width, us)
+    if pk.get("head_prep"):
+        us = pk["head_prep"] / LAYERS
+        moved = PROMPT * 4 * (n_lat * (heads * rot + rank + rot) + n_att * (heads + 2 * kv) * dim) / LAYERS
+        out["daferax_head_prep_us"], out["daferax_head_prep_hbm_frac"] = round(us, 2), hbm(moved, us)
+    if qk.get("qkv_rope_cache"):
+        us = qk["qkv_rope_cache"] / LAYERS
+        out["qwen2_rope_cache_us"], out["qwen2_rope_cache_hbm_frac"] = round(us, 2), hbm(PROMPT * 4 * (heads + 2 * kv) * dim, us)
+    for name in ("moe_gate_up", "moe_down"):
+        if pk.get(name):
+            share = 2.0 / 3.0 if name == "moe_gate_up" else 1.0 / 3.0
+            out[f"daferax_{name}_prefill_us"] = round(pk[name] / LAYERS, 1)
+            out[f"daferax_{name}_prefill_bf16_frac"] = tf(share * 6.0 * PROMPT * top * width * eff * LAYERS, pk[name])
+        if dk.get(name):
+            share = 2.0 / 3.0 if name == "moe_gate_up" else 1.0 / 3.0
+            touched = min(experts, 8 * top)
+            out[f"daferax_{name}_decode_us"] = round(dk[name] / LAYERS, 2)
+            out[f"daferax_{name}_decode_hbm_frac"] = hbm(share * touched * 3 * width * eff * 2 * LAYERS, dk[name])
+    for tag, prof in (("prefill", pk), ("decode_b8", dk)):
+        out[f"daferax_{tag}_small_kernels_us"] = {k: round(v / LAYERS, 2) for k, v in prof.items()
+                                                  if k in ("moe_route", "moe_plan", "moe_combine", "router_logits",
+                                                           "sigmoid_gate", "gemm_simt_batched")}
+    return out
+
+
 def _measure(cfg: dict, note) -> Dict[str, object]:
     import torch
     from ..ops import kernels as K
@@ -163,7 +268,23 @@ def _kernel_rooflines(size, res: Dict[str, Dict[str, object]], peaks) -> Dict[st
     return out
 
 
-def run(peaks, note=lambda m: None, sizes=None) -> Dict[str, object]:
+def run(peaks, note=lambda m: None, sizes=None, design: str = "dezelorn") -> Dict[str, object]:
+    if design == "daferax":
+        result = {"compare": "daferax vs qwen2 at equal layer sizes", "layers": LAYERS, "prompt": PROMPT,
+                  "decode_context": CONTEXT, "window": WINDOW, "vocab": VOCAB, "dtype": "bf16",
+                  "data": "synthetic: random weights, token ids uniform over the vocabulary",
+                  "peaks": peaks.get("source"), "sizes": {}}
+        for size in (sizes or DAFERAX_SIZES):
+            dims = DAFERAX_SIZES[size]
+            res = {}
+            for arch, make in (("daferax", daferax_config), ("qwen2", qwen2_like_daferax)):
+                note(f"{size}: {arch}")
+                res[arch] = _measure(make(*dims), note)
+            res["kernels"] = _daferax_rooflines(size, res, peaks)
+            res["dims"] = dict(zip(("width", "heads", "kv_heads", "head_dim", "kv_rank", "rot_dim", "experts",
+                                    "groups", "keep", "top", "expert_ff", "shared_ff"), dims))
+            result["sizes"][size] = res
+        return result
     result = {"compare": "dezelorn vs qwen2 at equal layer sizes", "layers": LAYERS, "prompt": PROMPT,
               "decode_context": CONTEXT, "window": WINDOW, "vocab": VOCAB, "dtype": "bf16",
               "data": "synthetic: random weights, token ids uniform over the vocabulary",

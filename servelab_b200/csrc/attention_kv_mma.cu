@@ -1,0 +1,276 @@
+// Tensor-core paged attention (bf16, mma.sync m16n8k16, float32 softmax and accumulation) for
+// mixers whose keys and values differ in size, compiled for one pair of sizes (SLB_KEY_DIM,
+// SLB_VALUE_DIM: multiples of 16, at most 320 and 256).  It serves prompt portions and single
+// tokens alike, and the absorbed form of a latent attention: with `tied` the values are the
+// first SLB_VALUE_DIM elements of the cached key rows, so a tile is fetched once and read by
+// both products.
+//
+// Work unit: (tile of 64 flattened query rows rho = local_token * g + head_in_group, kv head);
+// a warp owns 16 rows.  Keys are visited in tiles of 64 aligned to absolute positions through a
+// two-stage cp.async ring; Q fragments are re-read from shared memory k-step by k-step, so large
+// key sizes cost no registers; scores and the online softmax live in registers in the base-2
+// domain; P is rounded to bf16 as the operand of P.V.  Optional epilogue: head h's row times
+// sigmoid(gate[token][h]).
+//
+// In a step of single tokens a tile holds the g query heads of one request that share the kv
+// head (all heads of a latent attention): the rows of the MMA are heads.
+#include "mma_util.cuh"
+
+#ifndef SLB_KEY_DIM
+#error "compile with -DSLB_KEY_DIM=<key size> -DSLB_VALUE_DIM=<value size>"
+#endif
+
+SLB_DEFINE_PDL_SWITCH
+
+namespace {
+
+constexpr int DK = SLB_KEY_DIM, DV = SLB_VALUE_DIM;
+static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 320 && DV <= 256,
+              "key and value sizes must be multiples of 16, at most 320 and 256");
+constexpr int LDK = DK + 8, LDV = DV + 8;      // shared-memory row strides (16-byte pad)
+constexpr int BM = 64, BN = 64, NTHREADS = 128;
+constexpr int KCH = DK / 8, VCH = DV / 8;      // 16-byte chunks per row
+constexpr int KSTEPS = DK / 16, NT_O = DV / 8, NT_S = BN / 8;
+constexpr int STAGE_ELEMS = BN * LDK + BN * LDV;
+
+using namespace slb_mma;
+
+__device__ int kv_attn_status_word = 0;
+
+__device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc,
+                                          const bf16* __restrict__ vc, bool tied,
+                                          const int* __restrict__ table, int k0, int kend, int kvh,
+                                          int Hkv, int ps, int num_pages) {
+    const int per_row = tied ? KCH : KCH + VCH;
+    for (int idx = threadIdx.x; idx < BN * per_row; idx += NTHREADS) {
+        const int r = idx / per_row, c = idx - r * per_row;
+        const int kp = k0 + r;
+        bool ok = kp < kend;
+        int page = -1;
+        if (ok) page = table[kp / ps];
+        if (page >= num_pages) {
+            atomicCAS(&kv_attn_status_word, 0, 0x40);
+            page = -1;
+        }
+        ok = ok && page >= 0;
+        const size_t slot = ok ? ((size_t)page * Hkv + kvh) * ps + kp % ps : 0;
+        if (c < KCH) cp_async16(Ks + r * LDK + c * 8, kc + slot * DK + c * 8, ok);
+        else cp_async16(Vs + r * LDV + (c - KCH) * 8, vc + slot * DV + (c - KCH) * 8, ok);
+    }
+}
+
+__global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
+    const bf16* __restrict__ q, int ldq, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+    int tied, bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
+    const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
+    const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
+    int window, const bf16* __restrict__ gate, int ldg) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_wait();
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDK]
+    bf16* stage0 = Qs + BM * LDK;                          // 2 x (K tile | V tile)
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x % Hkv;
+    const int tile = (int)(gridDim.x / Hkv) - 1 - (int)(blockIdx.x / Hkv);   // the longest first
+    const int s = tile_seq[tile];
+    const int row0 = tile_row0[tile];
+    const int g = H / Hkv;
+    const int q0 = cu_q[s];
+    const int qlen = cu_q[s + 1] - q0;
+    const int ctx = ctx_len[s];
+    const int nrows = min(BM, qlen * g - row0);
+    if (nrows <= 0) return;
+    const int pos_base = ctx - qlen;
+    const int* table = block_table + (size_t)s * max_pages;
+
+    for (int idx = tid; idx < BM * KCH; idx += NTHREADS) {
+        const int r = idx / KCH, c = idx - r * KCH;
+        const bool ok = r < nrows;
+        const int rho = row0 + (ok ? r : 0);
+        const int tl = rho / g, hg = rho - tl * g;
+        cp_async16(Qs + r * LDK + c * 8, q + (size_t)(q0 + tl) * ldq + (size_t)(kvh * g + hg) * DK + c * 8, ok);
+    }
+    cp_async_commit();
+
+    const int p_first = pos_base + row0 / g;
+    const int p_last = pos_base + (row0 + nrows - 1) / g;
+    int kbeg = 0;
+    if (window > 0) kbeg = max(0, p_first - window + 1) / BN * BN;
+    const int kend = p_last + 1;
+    const int ntiles = (kend - kbeg + BN - 1) / BN;
+
+    load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages);
+    cp_async_commit();
+
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int pos_lo = r_lo < nrows ? pos_base + (row0 + r_lo) / g : -1;
+    const int pos_hi = r_hi < nrows ? pos_base + (row0 + r_hi) / g : -1;
+    const int wr_last = min(nrows - 1, warp * 16 + 15);
+    const int warp_pos_max = warp * 16 < nrows ? pos_base + (row0 + wr_last) / g : -1;
+    const int warp_pos_min = pos_base + (row0 + warp * 16) / g;
+    const int tig = lane & 3;
+
+    float o[NT_O][4];
+#pragma unroll
+    for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const bf16* Qw = Qs + warp * 16 * LDK;
+
+    for (int t = 0; t < ntiles; ++t) {
+        bf16* Ks = stage0 + (t & 1) * STAGE_ELEMS;
+        const bf16* Vs = tied ? Ks : Ks + BN * LDK;
+        const int ldv_s = tied ? LDK : LDV;
+        if (t + 1 < ntiles) {
+            bf16* Kn = stage0 + ((t + 1) & 1) * STAGE_ELEMS;
+            load_tile(Kn, Kn + BN * LDK, kc, vc, tied != 0, table, kbeg + (t + 1) * BN, kend, kvh, Hkv, ps,
+                      num_pages);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int k0 = kbeg + t * BN;
+        // (a warp whose rows all lie before the tile, or beyond the window's reach of it, skips it)
+        if (k0 <= warp_pos_max && (window <= 0 || warp_pos_min - (k0 + BN - 1) < window)) {
+            float sc[NT_S][4];
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
+#pragma unroll 2
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+                unsigned a[4];
+                ldmatrix_x4(a, Qw + (lane & 15) * LDK + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int jp = 0; jp < NT_S / 2; ++jp) {
+                    unsigned b[4];
+                    ldmatrix_x4(b, Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + kk * 16 +
+                                       ((lane >> 3) & 1) * 8);
+                    mma_bf16(sc[2 * jp], a, b[0], b[1]);
+                    mma_bf16(sc[2 * jp + 1], a, b[2], b[3]);
+                }
+            }
+            // mask, online softmax (base-2 domain)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < NT_S; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int kp = k0 + j * 8 + tig * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_lo : pos_hi;
+                    const bool vis = kp < kend && kp <= pos && (window <= 0 || pos - kp < window);
+                    if (!vis) sc[j][e] = -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sc[j][e]);
+                }
+            float alpha[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m[h], mx[h] * scale_log2);
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                alpha[h] = exp2f(m[h] - m_use);
+                m[h] = m_new;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < NT_S; ++j) {
+                    sc[j][2 * h] = exp2f(fmaf(sc[j][2 * h], scale_log2, -m_use));
+                    sc[j][2 * h + 1] = exp2f(fmaf(sc[j][2 * h + 1], scale_log2, -m_use));
+                    sum += sc[j][2 * h] + sc[j][2 * h + 1];
+                }
+                l[h] = l[h] * alpha[h] + sum;
+            }
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                for (int n = 0; n < NT_O; ++n) {
+                    o[n][0] *= alpha[0];
+                    o[n][1] *= alpha[0];
+                    o[n][2] *= alpha[1];
+                    o[n][3] *= alpha[1];
+                }
+            }
+            // O += P . V
+#pragma unroll
+            for (int ks = 0; ks < NT_S / 2; ++ks) {
+                unsigned a[4];
+                a[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+                a[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+                a[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+                a[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+                for (int np = 0; np < NT_O / 2; ++np) {
+                    unsigned b[4];
+                    ldmatrix_x4_trans(b, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + np * 16 +
+                                             (lane >> 4) * 8);
+                    mma_bf16(o[2 * np], a, b[0], b[1]);
+                    mma_bf16(o[2 * np + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    pdl_launch_dependents();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = h ? r_hi : r_lo;
+        if (row >= nrows) continue;
+        const int rho = row0 + row;
+        const int tl = rho / g, hg = rho - tl * g;
+        const int head = kvh * g + hg;
+        float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
+        if (gate != nullptr) {
+            const float z = __bfloat162float(gate[(size_t)(q0 + tl) * ldg + head]);
+            inv *= 1.0f / (1.0f + __expf(-z));
+        }
+        bf16* dst = out + (size_t)(q0 + tl) * ldo + (size_t)head * DV + tig * 2;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+            *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * h] * inv, o[n][2 * h + 1] * inv);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+int slb_attention_kv_mma_key_dim() { return DK; }
+int slb_attention_kv_mma_value_dim() { return DV; }
+int slb_attention_kv_mma_tile_rows() { return BM; }
+int slb_attention_kv_mma_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, kv_attn_status_word, sizeof(int)) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(kv_attn_status_word, &zero, sizeof(int));
+    }
+    return v;
+}
+// `tied`: the values are the first DV elements of the key rows (vc is ignored).
+int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16* vc, int tied, bf16* out,
+                              int ldo, const int* block_table, int max_pages, const int* cu_q,
+                              const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
+                              int H, int Hkv, int ps, int num_pages, float scale, int window,
+                              const bf16* gate, int ldg, cudaStream_t st) {
+    if (num_tiles <= 0) return 0;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
+        (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0)
+        return SLB_ERR_BAD_ARG;
+    if ((long long)num_tiles * Hkv > 2147483647LL) return SLB_ERR_TOO_LARGE;
+    const size_t smem = ((size_t)BM * LDK + 2 * STAGE_ELEMS) * sizeof(bf16);
+    static unsigned long long configured = 0;
+    const int rc = slb_configure(&configured, attention_kv_mma_kernel, smem);
+    if (rc != 0) return rc;
+    return slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv), dim3(NTHREADS), smem, st, q, ldq, kc,
+                      tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
+                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window, gate, ldg);
+}
+}

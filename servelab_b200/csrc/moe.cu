@@ -16,7 +16,7 @@
 // Each output element of a product is a sum over k = 0..K-1 in that order (plain FFMA), and the
 // combine adds a token's experts in the order of its choice, so a token's result does not depend
 // on what else is in the batch.
-#include "common.cuh"
+#include "mma_util.cuh"
 
 #define MOE_MAX_EXPERTS 1024
 #define MOE_MAX_TOP 32
@@ -246,6 +246,128 @@ __global__ void __launch_bounds__(256) moe_product_kernel(
     }
 }
 
+// ------------------------------------------------- products on tensor cores
+// The same two products in bfloat16 on mma.sync (m16n8k16, float32 accumulation): a block owns
+// 64 sorted rows of one expert and 64 output columns (MODE 0: 64 gate columns AND their 64 up
+// columns, the activation in the epilogue), a warp 16 rows; A rows (gathered by the plan) and W
+// rows arrive by 16-byte cp.async through a two-stage ring of 32-element k-blocks.  Rows, K and
+// the leading dimensions must be multiples of 8 elements.
+#define MM_BM 64
+#define MM_BN 64
+#define MM_BK 32
+#define MM_LD (MM_BK + 8)
+
+template <int MODE>
+__global__ void __launch_bounds__(128) moe_product_mma_kernel(
+    const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, long long w_expert_stride, int ldw,
+    void* __restrict__ Cv, int ldc, const int* __restrict__ plan, int E, int num_tiles, int top, int N,
+    int K) {
+    using namespace slb_mma;
+    __shared__ __align__(16) bf16 As[2][MM_BM][MM_LD];
+    __shared__ __align__(16) bf16 Ws[2][MM_BN][MM_LD];
+    __shared__ __align__(16) bf16 Us[MODE == 0 ? 2 : 1][MODE == 0 ? MM_BN : 1][MM_LD];
+    __shared__ int rows[MM_BM];
+    pdl_wait();
+    const int* counts = plan;
+    const int* offsets = plan + E;
+    const int* tile_expert = offsets + E + 1 + E;
+    const int* tile_row0 = tile_expert + num_tiles;
+    const int* sorted = tile_row0 + num_tiles;
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    const int r0 = tile_row0[blockIdx.y];
+    const int nrows = min(MM_BM, counts[e] - r0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid < MM_BM) rows[tid] = tid < nrows ? sorted[offsets[e] + r0 + tid] : -1;
+    __syncthreads();
+    const bf16* We = W + (size_t)e * w_expert_stride;
+    const int n0 = blockIdx.x * MM_BN;
+
+    auto load = [&](int stage, int k0) {
+        // 64 rows x 4 chunks of 8 elements for each of A, W (and U)
+        for (int idx = tid; idx < MM_BM * 4; idx += 128) {
+            const int r = idx >> 2, c = idx & 3;
+            const int gk = k0 + c * 8;
+            const int pr = rows[r];
+            const bool oka = pr >= 0 && gk < K;
+            cp_async16(&As[stage][r][c * 8], A + (oka ? (size_t)(MODE == 0 ? pr / top : pr) * lda + gk : 0), oka);
+            const bool okw = n0 + r < N && gk < K;
+            cp_async16(&Ws[stage][r][c * 8], We + (okw ? (size_t)(n0 + r) * ldw + gk : 0), okw);
+            if (MODE == 0)
+                cp_async16(&Us[stage][r][c * 8], We + (okw ? (size_t)(N + n0 + r) * ldw + gk : 0), okw);
+        }
+    };
+
+    float acc[MM_BN / 8][4], acu[MODE == 0 ? MM_BN / 8 : 1][4];
+#pragma unroll
+    for (int j = 0; j < MM_BN / 8; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acc[j][x] = 0.f;
+#pragma unroll
+    for (int j = 0; j < (MODE == 0 ? MM_BN / 8 : 1); ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) acu[j][x] = 0.f;
+
+    const int nk = (K + MM_BK - 1) / MM_BK;
+    load(0, 0);
+    cp_async_commit();
+    const bool active = warp * 16 < nrows;
+    for (int kb = 0; kb < nk; ++kb) {
+        if (kb + 1 < nk) {
+            load((kb + 1) & 1, (kb + 1) * MM_BK);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int st = kb & 1;
+        if (active) {
+#pragma unroll
+            for (int kk = 0; kk < MM_BK / 16; ++kk) {
+                unsigned a[4];
+                ldmatrix_x4(a, &As[st][warp * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]);
+#pragma unroll
+                for (int jp = 0; jp < MM_BN / 16; ++jp) {
+                    unsigned b[4];
+                    ldmatrix_x4(b, &Ws[st][jp * 16 + (lane >> 4) * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]);
+                    mma_bf16(acc[2 * jp], a, b[0], b[1]);
+                    mma_bf16(acc[2 * jp + 1], a, b[2], b[3]);
+                    if (MODE == 0) {
+                        ldmatrix_x4(b, &Us[st][jp * 16 + (lane >> 4) * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]);
+                        mma_bf16(acu[2 * jp], a, b[0], b[1]);
+                        mma_bf16(acu[2 * jp + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+    const int tig = lane & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int pr = rows[warp * 16 + (lane >> 2) + 8 * h];
+        if (pr < 0) continue;
+#pragma unroll
+        for (int j = 0; j < MM_BN / 8; ++j) {
+            const int gn = n0 + j * 8 + tig * 2;
+            if (gn >= N) continue;                        // (N is even: both columns exist or neither)
+            float v0 = acc[j][2 * h], v1 = acc[j][2 * h + 1];
+            if (MODE == 0) {
+                const float g0 = __bfloat162float(__float2bfloat16_rn(v0)), g1 = __bfloat162float(__float2bfloat16_rn(v1));
+                const float u0 = __bfloat162float(__float2bfloat16_rn(acu[j][2 * h]));
+                const float u1 = __bfloat162float(__float2bfloat16_rn(acu[j][2 * h + 1]));
+                v0 = g0 / (1.0f + expf(-g0)) * u0;
+                v1 = g1 / (1.0f + expf(-g1)) * u1;
+                *reinterpret_cast<unsigned*>(reinterpret_cast<bf16*>(Cv) + (size_t)pr * ldc + gn) = pack_bf16(v0, v1);
+            } else {
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(Cv) + (size_t)pr * ldc + gn) = make_float2(v0, v1);
+            }
+        }
+    }
+}
+
 // ----------------------------------------------------------------- combine
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(
@@ -286,7 +408,28 @@ static int launch_moe_down(const T* act, int lda, const T* w_down, int ldw, floa
                       act, lda, w_down, (long long)N * ldw, ldw, y, ldy, plan, E, nt, P, top, N, I);
 }
 
+template <int MODE>
+static int launch_moe_mma(const bf16* A, int lda, const bf16* W, long long stride, int ldw, void* C, int ldc,
+                          const int* plan, int E, int P, int top, int N, int K, cudaStream_t st) {
+    if (P <= 0) return 0;
+    if (E <= 0 || top <= 0 || N <= 0 || K <= 0 || K % 8 || lda % 8 || ldw % 8 || N % 2 || ldc % 2 ||
+        ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || (stride % 8))
+        return SLB_ERR_BAD_ARG;
+    const int nt = moe_num_tiles(P, E);
+    if (nt > 65535) return SLB_ERR_TOO_LARGE;
+    return slb_launch(moe_product_mma_kernel<MODE>, dim3((N + MM_BN - 1) / MM_BN, nt), dim3(128), 0, st, A, lda,
+                      W, stride, ldw, C, ldc, plan, E, nt, top, N, K);
+}
+
 extern "C" {
+int slb_moe_gate_up_mma_bf16(const bf16* x, int ldx, const bf16* w_gu, int ldw, bf16* act, int lda,
+                             const int* plan, int E, int P, int top, int I, int K, cudaStream_t st) {
+    return launch_moe_mma<0>(x, ldx, w_gu, (long long)2 * I * ldw, ldw, act, lda, plan, E, P, top, I, K, st);
+}
+int slb_moe_down_mma_bf16(const bf16* act, int lda, const bf16* w_down, int ldw, float* y, int ldy,
+                          const int* plan, int E, int P, int top, int N, int I, cudaStream_t st) {
+    return launch_moe_mma<1>(act, lda, w_down, (long long)N * ldw, ldw, y, ldy, plan, E, P, top, N, I, st);
+}
 int slb_moe_tile_rows() { return MOE_BM; }
 int slb_moe_route(const float* logits, int ldl, int T, int E, int groups, int keep, int top,
                   float route_scale, int renormalize, int* ids, float* weights, cudaStream_t st) {

@@ -107,14 +107,33 @@ def check_kv_supported(key_dim: int, value_dim: int) -> None:
                             f"1..{KV_MAX_VALUE_DIM} elements, got {key_dim} and {value_dim}")
 
 
+use_kv_fast = True         # bfloat16: the tensor-core kernel (off: the plain kernel, its twin)
+KV_FAST_MAX_KEY_DIM, KV_FAST_MAX_VALUE_DIM = 320, 256
+
+
+def _kv_fast(key_dim: int, value_dim: int, dtype: torch.dtype) -> bool:
+    return (dtype == torch.bfloat16 and use_kv_fast and not force_generic
+            and key_dim % 16 == 0 and value_dim % 16 == 0
+            and key_dim <= KV_FAST_MAX_KEY_DIM and value_dim <= KV_FAST_MAX_VALUE_DIM)
+
+
 def prepare_kv_attention(key_dim: int, value_dim: int, dtype: torch.dtype) -> None:
     """Builds what ``kv_attention`` will launch for these sizes (at load, not in a step)."""
+    if _kv_fast(key_dim, value_dim, dtype) and torch.cuda.is_available():
+        L.attention_kv(key_dim, value_dim)
 
 
 def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
                  window, head_gate) -> None:
     """Attention with keys of ``Dk`` and values of ``Dv`` elements (value rows ``v_row_stride``
-    apart in ``v_cache``, which may be the key cache), causal with an optional window, head h's
-    row times sigmoid(head_gate[t, h]) if given."""
+    apart in ``v_cache``, which may be the key cache: the values are then a prefix of the key
+    rows), causal with an optional window, head h's row times sigmoid(head_gate[t, h]) if given.
+    float32, or sizes the tensor-core kernel does not take: the plain kernel."""
+    tied = v_cache.data_ptr() == k_cache.data_ptr() and v_row_stride == Dk
+    if _kv_fast(Dk, Dv, q.dtype) and (tied or v_row_stride == Dv) and q.stride(0) % 8 == 0 \
+            and out.stride(0) % 2 == 0:
+        K.attention_kv_mma(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
+                           window, head_gate)
+        return
     K.attention_kv(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk, Dv, page_size, scale,
                    window, head_gate)

@@ -919,6 +919,24 @@ def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, 
                _stream()), "attention_kv")
 
 
+def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
+                     num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
+                     head_gate: Optional[torch.Tensor] = None) -> None:
+    """The tensor-core kernel (bfloat16), for prompt portions and single tokens."""
+    lib = L.attention_kv(k_dim, v_dim)
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, lib.slb_attention_kv_mma_tile_rows())
+    L.check(lib.slb_attention_kv_mma_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
+        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+        ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
+        page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
+        head_gate.stride(0) if head_gate is not None else 0, _stream()), "attention_kv_mma")
+
+
+def attention_kv_mma_status(k_dim: int, v_dim: int, reset: bool = False) -> int:
+    return L.attention_kv(k_dim, v_dim).slb_attention_kv_mma_status(1 if reset else 0)
+
+
 # ----------------------------------------------------- per-head batches of products
 def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[:, b, :] = a[:, b, :] . w[b]^T for a [M, B, K], w [B, N, K], out [M, B, N] (views with
@@ -954,6 +972,9 @@ def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, route_scal
     return ids, weights
 
 
+moe_tensor_cores = True        # bfloat16: the experts' products on mma.sync (off: CUDA cores, the twin)
+
+
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, shared: Optional[torch.Tensor]) -> torch.Tensor:
     """sum_k weights[t, k] * down_e(silu(gate_e x_t) * up_e x_t) (+ shared[t]), e = ids[t, k];
@@ -968,11 +989,15 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     L.check(lib.slb_moe_plan(ids.data_ptr(), P, E, plan.data_ptr(), _stream()), "moe_plan")
     act = torch.empty((P, inter), dtype=x.dtype, device=x.device)
     sfx = _suffix(x.dtype)
-    L.check(getattr(lib, "slb_moe_gate_up_" + sfx)(
+    # bfloat16 with rows of whole 16-byte chunks: the tensor-core products; else CUDA cores
+    mma = (x.dtype == _BF16 and moe_tensor_cores and h % 8 == 0 and inter % 8 == 0 and n_out % 2 == 0
+           and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
+    up_sfx = "mma_bf16" if mma else sfx
+    L.check(getattr(lib, "slb_moe_gate_up_" + up_sfx)(
         x.data_ptr(), x.stride(0), w_gate_up.data_ptr(), w_gate_up.stride(1), act.data_ptr(), act.stride(0),
         plan.data_ptr(), E, P, top, inter, h, _stream()), "moe_gate_up")
     y = torch.empty((P, n_out), dtype=_F32, device=x.device)
-    L.check(getattr(lib, "slb_moe_down_" + sfx)(
+    L.check(getattr(lib, "slb_moe_down_" + up_sfx)(
         act.data_ptr(), act.stride(0), w_down.data_ptr(), w_down.stride(1), y.data_ptr(), y.stride(0),
         plan.data_ptr(), E, P, top, n_out, inter, _stream()), "moe_down")
     out = torch.empty((T, n_out), dtype=x.dtype, device=x.device)

@@ -82,6 +82,8 @@ _CORE_SIGNATURES = {
     "slb_moe_gate_up_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
     "slb_moe_down_f32": [P, I, P, I, P, I, P, I, I, I, I, I, P],
     "slb_moe_down_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_gate_up_mma_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
+    "slb_moe_down_mma_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
     "slb_moe_combine_f32": [P, I, P, P, I, P, I, I, I, I, P],
     "slb_moe_combine_bf16": [P, I, P, P, I, P, I, I, I, I, P],
 }
@@ -224,6 +226,33 @@ def attention(head_dim: int) -> ctypes.CDLL:
         if lib.slb_attention_head_dim() != head_dim:
             raise KernelsUnavailable(f"attention library built for head size "
                                      f"{lib.slb_attention_head_dim()}, wanted {head_dim}")
+        _apply_switches(lib)
+        _libs[key] = lib
+    return lib
+
+
+_ATTN_KV_SIGNATURES = {
+    "slb_attention_kv_mma_key_dim": [],
+    "slb_attention_kv_mma_value_dim": [],
+    "slb_attention_kv_mma_tile_rows": [],
+    "slb_attention_kv_mma_status": [I],
+    "slb_attention_kv_mma_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, P],
+}
+
+
+def attention_kv(key_dim: int, value_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention kernels for keys of ``key_dim`` and values of ``value_dim``."""
+    key = f"attn_k{key_dim}v{value_dim}"
+    lib = _libs.get(key)
+    if lib is None:
+        try:
+            lib = ctypes.CDLL(_build.attention_kv_library(key_dim, value_dim))
+        except (OSError, _build.BuildError) as e:
+            raise KernelsUnavailable(f"the attention kernels for key size {key_dim} and value size "
+                                     f"{value_dim} are not available: {e}") from e
+        _declare(lib, _ATTN_KV_SIGNATURES, True)
+        if (lib.slb_attention_kv_mma_key_dim(), lib.slb_attention_kv_mma_value_dim()) != (key_dim, value_dim):
+            raise KernelsUnavailable("attention library built for other sizes than asked for")
         _apply_switches(lib)
         _libs[key] = lib
     return lib

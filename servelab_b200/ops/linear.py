@@ -211,4 +211,4 @@ def batched_head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> 
     _mark("library gemm")
 
 
-use_vendor_batched = False
+use_vendor_batched = True

@@ -66,6 +66,10 @@ STD_OF = {"embed": 0.5, ".mix.q": 0.3, ".mix.k": 0.3, ".mix.dkv": 0.3, ".mix.uk"
 
 
 def make_model(folder: str, cfg: dict, seed: int) -> str:
+    """The weights are stored in bfloat16, as a served model's are: what the engine's bfloat16 path
+    computes then differs from the oracle by the rounding of activations only."""
+    import torch
     from servelab_b200.config import config_from_dict
     from servelab_b200.weights import write_random_model
-    return write_random_model(folder, config_from_dict(cfg), seed, std=0.15, norm_std=0.3, std_of=STD_OF)
+    return write_random_model(folder, config_from_dict(cfg), seed, dtype=torch.bfloat16, std=0.15,
+                              norm_std=0.3, std_of=STD_OF)
