@@ -12,6 +12,10 @@
 // domain; P is rounded to bf16 as the operand of P.V.  Optional epilogue: head h's row times
 // sigmoid(gate[token][h]).
 //
+// Steps of few single tokens split every request's keys over `splits` blocks (grid y): a block
+// leaves its unnormalised rows with their running maxima and sums in scratch, and a second small
+// kernel combines them (and applies the gate).
+//
 // In a step of single tokens a tile holds the g query heads of one request that share the kv
 // head (all heads of a latent attention): the rows of the MMA are heads.
 #include "mma_util.cuh"
@@ -28,10 +32,12 @@ constexpr int DK = SLB_KEY_DIM, DV = SLB_VALUE_DIM;
 static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 320 && DV <= 256,
               "key and value sizes must be multiples of 16, at most 320 and 256");
 constexpr int LDK = DK + 8, LDV = DV + 8;      // shared-memory row strides (16-byte pad)
-constexpr int BM = 64, BN = 64, NTHREADS = 128;
+// (keys per tile: 32 for large keys, so that two blocks fit an SM's shared memory)
+constexpr int BM = 64, BN = SLB_KEY_DIM > 192 ? 32 : 64, NTHREADS = 128;
 constexpr int KCH = DK / 8, VCH = DV / 8;      // 16-byte chunks per row
 constexpr int KSTEPS = DK / 16, NT_O = DV / 8, NT_S = BN / 8;
-constexpr int STAGE_ELEMS = BN * LDK + BN * LDV;
+// a stage of the ring: a K tile and, unless the values are part of the key rows, a V tile
+__host__ __device__ constexpr int stage_elems(bool tied) { return BN * LDK + (tied ? 0 : BN * LDV); }
 
 using namespace slb_mma;
 
@@ -64,11 +70,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     int tied, bf16* __restrict__ out, int ldo, const int* __restrict__ block_table, int max_pages,
     const int* __restrict__ cu_q, const int* __restrict__ ctx_len, const int* __restrict__ tile_seq,
     const int* __restrict__ tile_row0, int H, int Hkv, int ps, int num_pages, float scale_log2,
-    int window, const bf16* __restrict__ gate, int ldg) {
+    int window, const bf16* __restrict__ gate, int ldg, int splits, float* __restrict__ part_o,
+    float* __restrict__ part_ml) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     pdl_wait();
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [BM][LDK]
     bf16* stage0 = Qs + BM * LDK;                          // 2 x (K tile | V tile)
+    const int STAGE_ELEMS = stage_elems(tied != 0);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x % Hkv;
@@ -98,9 +106,16 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     int kbeg = 0;
     if (window > 0) kbeg = max(0, p_first - window + 1) / BN * BN;
     const int kend = p_last + 1;
-    const int ntiles = (kend - kbeg + BN - 1) / BN;
+    int ntiles = (kend - kbeg + BN - 1) / BN;
+    if (splits > 1) {                                      // this block's share of the key tiles
+        const int per = (ntiles + splits - 1) / splits;
+        const int first = min(ntiles, (int)blockIdx.y * per);
+        ntiles = min(ntiles, first + per) - first;
+        kbeg += first * BN;
+    }
 
-    load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages);
+    if (ntiles > 0)
+        load_tile(stage0, stage0 + BN * LDK, kc, vc, tied != 0, table, kbeg, kend, kvh, Hkv, ps, num_pages);
     cp_async_commit();
 
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -214,6 +229,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         __syncthreads();
     }
 
+    cp_async_wait<0>();                                    // (a block without key tiles fetched Q all the same)
     pdl_launch_dependents();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -227,6 +243,18 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
         const int rho = row0 + row;
         const int tl = rho / g, hg = rho - tl * g;
         const int head = kvh * g + hg;
+        if (splits > 1) {
+            const size_t pi = ((size_t)(q0 + tl) * H + head) * splits + blockIdx.y;
+            if (tig == 0) {
+                part_ml[2 * pi] = m[h];
+                part_ml[2 * pi + 1] = l[h];
+            }
+            float* po = part_o + pi * DV + tig * 2;
+#pragma unroll
+            for (int n = 0; n < NT_O; ++n)
+                *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+            continue;
+        }
         float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
         if (gate != nullptr) {
             const float z = __bfloat162float(gate[(size_t)(q0 + tl) * ldg + head]);
@@ -239,9 +267,48 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
     }
 }
 
+// out[t][h] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) (times the gate): one block a (token,
+// head), a thread two neighbouring columns; the splits' weights are formed once per block.
+__global__ void __launch_bounds__(128) attention_kv_combine_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, bf16* __restrict__ out,
+    int ldo, int H, const bf16* __restrict__ gate, int ldg) {
+    __shared__ float wgt[32];
+    __shared__ float inv_s;
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t t = blockIdx.x;
+    const int head = blockIdx.y;
+    const size_t base = (t * H + head) * splits;
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        const float ms = s < splits ? part_ml[2 * (base + s)] : -INFINITY;
+        const float ls = s < splits ? part_ml[2 * (base + s) + 1] : 0.f;
+        const float M = warp_max(ms);
+        const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        const float L = warp_sum(ls * w);
+        wgt[s] = w;
+        if (s == 0) {
+            float inv = L > 0.f ? 1.f / L : 0.f;
+            if (gate != nullptr) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[t * ldg + head])));
+            inv_s = inv;
+        }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x * 2; c < DV; c += blockDim.x * 2) {
+        float a0 = 0.f, a1 = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float2 v = *reinterpret_cast<const float2*>(part_o + (base + s) * DV + c);
+            a0 += v.x * wgt[s];
+            a1 += v.y * wgt[s];
+        }
+        *reinterpret_cast<unsigned*>(out + t * ldo + (size_t)head * DV + c) = pack_bf16(a0 * inv_s, a1 * inv_s);
+    }
+}
+
 }  // namespace
 
 extern "C" {
+int slb_attention_kv_mma_max_splits() { return 32; }
 int slb_attention_kv_mma_key_dim() { return DK; }
 int slb_attention_kv_mma_value_dim() { return DV; }
 int slb_attention_kv_mma_tile_rows() { return BM; }
@@ -259,18 +326,29 @@ int slb_attention_kv_mma_bf16(const bf16* q, int ldq, const bf16* kc, const bf16
                               int ldo, const int* block_table, int max_pages, const int* cu_q,
                               const int* ctx_len, const int* tile_seq, const int* tile_row0, int num_tiles,
                               int H, int Hkv, int ps, int num_pages, float scale, int window,
-                              const bf16* gate, int ldg, cudaStream_t st) {
+                              const bf16* gate, int ldg, int splits, float* part_o, float* part_ml,
+                              cudaStream_t st) {
+    // `splits` > 1 (steps of single tokens only: a tile is one token's heads): scratch part_o
+    // [tokens][H][splits][DV] and part_ml [tokens][H][splits][2], float32.
     if (num_tiles <= 0) return 0;
+    if (splits < 1 || splits > 32 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || H / Hkv > BM)))
+        return SLB_ERR_BAD_ARG;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || ps <= 0 || max_pages <= 0 || num_pages <= 0 || scale <= 0.f ||
         (tied && DV > DK) || ldq % 8 != 0 || ldo % 2 != 0)
         return SLB_ERR_BAD_ARG;
     if ((long long)num_tiles * Hkv > 2147483647LL) return SLB_ERR_TOO_LARGE;
-    const size_t smem = ((size_t)BM * LDK + 2 * STAGE_ELEMS) * sizeof(bf16);
+    const size_t smem = ((size_t)BM * LDK + 2 * stage_elems(tied != 0)) * sizeof(bf16);
     static unsigned long long configured = 0;
-    const int rc = slb_configure(&configured, attention_kv_mma_kernel, smem);
+    const int rc = slb_configure(&configured, attention_kv_mma_kernel,
+                                 ((size_t)BM * LDK + 2 * stage_elems(false)) * sizeof(bf16));
     if (rc != 0) return rc;
-    return slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv), dim3(NTHREADS), smem, st, q, ldq, kc,
-                      tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len, tile_seq,
-                      tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window, gate, ldg);
+    const int e = slb_launch(attention_kv_mma_kernel, dim3(num_tiles * Hkv, splits), dim3(NTHREADS), smem, st, q,
+                             ldq, kc, tied ? kc : vc, tied, out, ldo, block_table, max_pages, cu_q, ctx_len,
+                             tile_seq, tile_row0, H, Hkv, ps, num_pages, scale * 1.4426950408889634f, window,
+                             gate, ldg, splits, part_o, part_ml);
+    if (e != 0 || splits == 1) return e;
+    // (one tile a token: num_tiles is the number of tokens)
+    return slb_launch(attention_kv_combine_kernel, dim3(num_tiles, H), dim3(128), 0, st, (const float*)part_o,
+                      (const float*)part_ml, splits, out, ldo, H, gate, ldg);
 }
 }

@@ -106,11 +106,6 @@ int slb_gemm_simt_batched_bf16(const bf16* A, int lda, const bf16* W, int ldw, b
     return launch_gemm<bf16, bf16, bf16>(A, lda, W, ldw, C, ldc, nullptr, M, N, K, st, batch, batch_a,
                                          batch_w, batch_c);
 }
-// bfloat16 activations against a float32 matrix, float32 result (a router's logits)
-int slb_gemm_simt_bf16_wf32(const bf16* A, int lda, const float* W, int ldw, float* C, int ldc,
-                            const float* bias, int M, int N, int K, cudaStream_t st) {
-    return launch_gemm<bf16, float, float>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);
-}
 int slb_gemm_simt_bf16_f32out(const bf16* A, int lda, const bf16* W, int ldw, float* C, int ldc,
                               const float* bias, int M, int N, int K, cudaStream_t st) {
     return launch_gemm<bf16, bf16, float>(A, lda, W, ldw, C, ldc, bias, M, N, K, st);

@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
     }
     const int nv = a.v_off >= 0 ? a.G : 0;
     const int units = a.H + a.G + nv;
-    for (int u = warp; u < units; u += HP_WARPS) {
+    // (grid y: groups of HP_WARPS vectors, so that a step of few tokens still fills the device)
+    for (int u = blockIdx.y * HP_WARPS + warp; u < units; u += gridDim.y * HP_WARPS) {
         const T* src;
         T* dst = nullptr;
         int D, norm_dims = 0, rot_off = 0;
@@ -154,7 +155,9 @@ static int launch_head_prep(const HeadPrepArgs& a, int num_tokens, cudaStream_t 
     if ((a.k_cache != nullptr || a.v_cache != nullptr) && (a.block_table == nullptr || a.page_size <= 0))
         return SLB_ERR_BAD_ARG;
     const size_t smem = (size_t)HP_WARPS * maxd * sizeof(float);
-    return slb_launch(head_prep_kernel<T>, dim3(num_tokens), dim3(HP_WARPS * 32), smem, st, a);
+    const int units = a.H + a.G + (a.v_off >= 0 ? a.G : 0);
+    const int gy = num_tokens < 512 ? (units + HP_WARPS - 1) / HP_WARPS : 1;
+    return slb_launch(head_prep_kernel<T>, dim3(num_tokens, gy), dim3(HP_WARPS * 32), smem, st, a);
 }
 
 extern "C" {

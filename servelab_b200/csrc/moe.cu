@@ -111,6 +111,52 @@ __global__ void __launch_bounds__(128) moe_route_kernel(
     }
 }
 
+// ----------------------------------------------------------- router logits
+// logits[t][e] = sum_k x[t][k] * w[e][k] in float32 (w float32, x float32 or bfloat16).  A block
+// owns ROUTER_TOK tokens and one expert; its eight warps take an eighth of k each (lanes stride,
+// coalesced) and the partial sums are added in a fixed order, so a token's logits do not depend
+// on the batch.
+#define ROUTER_TOK 4
+template <typename T>
+__global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict__ x, int ldx,
+                                                            const float* __restrict__ w, int ldw,
+                                                            float* __restrict__ logits, int ldl, int M,
+                                                            int E, int K) {
+    __shared__ float part[8][ROUTER_TOK];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * ROUTER_TOK;
+    const int e = blockIdx.y;
+    const T* xr[ROUTER_TOK];
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOK; ++i) xr[i] = x + (size_t)min(t0 + i, M - 1) * ldx;
+    const float* wr = w + (size_t)e * ldw;
+    const int per = (K + 7) / 8;
+    const int k_end = min(K, (warp + 1) * per);
+    float acc[ROUTER_TOK];
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOK; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int k = warp * per + lane; k < k_end; k += 32) {
+        const float wv = wr[k];
+#pragma unroll
+        for (int i = 0; i < ROUTER_TOK; ++i) acc[i] = fmaf(to_float(xr[i][k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTER_TOK; ++i) {
+        const float v = warp_sum(acc[i]);
+        if (lane == 0) part[warp][i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < ROUTER_TOK && t0 + threadIdx.x < M) {
+        float v = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v += part[j][threadIdx.x];
+        logits[(size_t)(t0 + threadIdx.x) * ldl + e] = v;
+    }
+}
+
 // -------------------------------------------------------------------- plan
 // One block.  plan = [counts E | offsets E + 1 | cursor E | tile_expert NT | tile_row0 NT |
 // sorted P] (int32), NT = ceil(P / MOE_BM) + E.
@@ -376,7 +422,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
         float v = 0.f;
         for (int k = 0; k < top; ++k) v += weights[(size_t)t * top + k] * y[((size_t)t * top + k) * ldy + c];
         if (shared != nullptr) v += to_float(shared[(size_t)t * lds + c]);
@@ -442,6 +488,20 @@ int slb_moe_route(const float* logits, int ldl, int T, int E, int groups, int ke
     return slb_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), smem, st, logits, ldl, T, E, groups,
                       keep, top, route_scale, renormalize, ids, weights);
 }
+int slb_router_logits_f32(const float* x, int ldx, const float* w, int ldw, float* logits, int ldl, int M,
+                          int E, int K, cudaStream_t st) {
+    if (M <= 0 || E <= 0) return 0;
+    if (K <= 0) return SLB_ERR_BAD_ARG;
+    return slb_launch(router_logits_kernel<float>, dim3((M + ROUTER_TOK - 1) / ROUTER_TOK, E), dim3(256), 0, st, x,
+                      ldx, w, ldw, logits, ldl, M, E, K);
+}
+int slb_router_logits_bf16(const bf16* x, int ldx, const float* w, int ldw, float* logits, int ldl, int M,
+                           int E, int K, cudaStream_t st) {
+    if (M <= 0 || E <= 0) return 0;
+    if (K <= 0) return SLB_ERR_BAD_ARG;
+    return slb_launch(router_logits_kernel<bf16>, dim3((M + ROUTER_TOK - 1) / ROUTER_TOK, E), dim3(256), 0, st, x,
+                      ldx, w, ldw, logits, ldl, M, E, K);
+}
 int slb_moe_plan_ints(int P, int E) { return 4 * E + 1 + 2 * moe_num_tiles(P, E) + P; }
 int slb_moe_plan(const int* ids, int P, int E, int* plan, cudaStream_t st) {
     if (P <= 0) return 0;
@@ -467,13 +527,13 @@ int slb_moe_down_bf16(const bf16* act, int lda, const bf16* w_down, int ldw, flo
 int slb_moe_combine_f32(const float* y, int ldy, const float* weights, const float* shared, int lds,
                         float* out, int ldo, int T, int top, int N, cudaStream_t st) {
     if (T <= 0) return 0;
-    return slb_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, st, y, ldy, weights, shared, lds,
+    return slb_launch(moe_combine_kernel<float>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
                       out, ldo, top, N);
 }
 int slb_moe_combine_bf16(const float* y, int ldy, const float* weights, const bf16* shared, int lds,
                          bf16* out, int ldo, int T, int top, int N, cudaStream_t st) {
     if (T <= 0) return 0;
-    return slb_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, st, y, ldy, weights, shared, lds,
+    return slb_launch(moe_combine_kernel<bf16>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
                       out, ldo, top, N);
 }
 }

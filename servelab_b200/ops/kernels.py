@@ -919,18 +919,43 @@ def attention_kv(ctx, q, k_cache, v_cache, v_row_stride: int, out, block_table, 
                _stream()), "attention_kv")
 
 
+def attention_kv_splits(num_seqs: int, num_kv_heads: int, longest_context: int, window: int,
+                        tile_keys: int = 64, max_splits: int = 32) -> int:
+    """Blocks a request's keys are split over in a step of single tokens: enough to fill the
+    device twice, at least two key tiles a block."""
+    seen = min(longest_context, window + tile_keys) if window > 0 else longest_context
+    tiles = -(-seen // tile_keys)
+    want = -(-2 * _num_sms() // max(1, num_seqs * num_kv_heads))
+    return max(1, min(max_splits, want, tiles // 2))
+
+
 def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
                      num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
                      head_gate: Optional[torch.Tensor] = None) -> None:
-    """The tensor-core kernel (bfloat16), for prompt portions and single tokens."""
+    """The tensor-core kernel (bfloat16), for prompt portions and single tokens; in a step of
+    single tokens the keys of a request are split over several blocks when the requests alone
+    would not fill the device."""
     lib = L.attention_kv(k_dim, v_dim)
-    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, lib.slb_attention_kv_mma_tile_rows())
+    rows = lib.slb_attention_kv_mma_tile_rows()
+    tile_seq, tile_row0, n = ctx.attention_tiles(num_heads // num_kv_heads, rows)
+    splits, part_o, part_ml = 1, None, None
+    if ctx.decode_only and attention_kv_split and num_heads // num_kv_heads <= rows:
+        splits = attention_kv_splits(ctx.num_seqs, num_kv_heads, ctx.split_hint_len, window,
+                                     max_splits=lib.slb_attention_kv_mma_max_splits())
+        if splits > 1:
+            T = q.shape[0]
+            part_o = torch.empty((T, num_heads, splits, v_dim), dtype=_F32, device=q.device)
+            part_ml = torch.empty((T, num_heads, splits, 2), dtype=_F32, device=q.device)
     L.check(lib.slb_attention_kv_mma_bf16(
         q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
         out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
         ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
         page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
-        head_gate.stride(0) if head_gate is not None else 0, _stream()), "attention_kv_mma")
+        head_gate.stride(0) if head_gate is not None else 0, splits, _p(part_o), _p(part_ml), _stream()),
+        "attention_kv_mma")
+
+
+attention_kv_split = True      # (off: one block a request and kv head, the twin)
 
 
 def attention_kv_mma_status(k_dim: int, v_dim: int, reset: bool = False) -> int:
@@ -949,12 +974,13 @@ def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> No
 
 
 def router_logits(x: torch.Tensor, w_f32: torch.Tensor) -> torch.Tensor:
-    """float32 logits x . w^T of a float32 router matrix (activations float32 or bfloat16)."""
+    """float32 logits x . w^T of a float32 router matrix (activations float32 or bfloat16); a
+    token's sums run in a fixed order."""
     M, Kd = x.shape
     out = torch.empty((M, w_f32.shape[0]), dtype=_F32, device=x.device)
-    fn = L.core().slb_gemm_simt_f32 if x.dtype == _F32 else L.core().slb_gemm_simt_bf16_wf32
+    fn = getattr(L.core(), "slb_router_logits_" + _suffix(x.dtype))
     L.check(fn(x.data_ptr(), x.stride(0), w_f32.data_ptr(), w_f32.stride(0), out.data_ptr(), out.stride(0),
-               None, M, w_f32.shape[0], Kd, _stream()), "router_logits")
+               M, w_f32.shape[0], Kd, _stream()), "router_logits")
     return out
 
 

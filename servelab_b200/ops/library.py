@@ -73,9 +73,10 @@ _CORE_SIGNATURES = {
     "slb_attention_kv_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
     "slb_gemm_simt_batched_f32": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
     "slb_gemm_simt_batched_bf16": [P, I, P, I, P, I, I, I, I, I, LL, LL, LL, P],
-    "slb_gemm_simt_bf16_wf32": [P, I, P, I, P, I, P, I, I, I, P],
     "slb_moe_tile_rows": [],
     "slb_moe_route": [P, I, I, I, I, I, I, F, I, P, P, P],
+    "slb_router_logits_f32": [P, I, P, I, P, I, I, I, I, P],
+    "slb_router_logits_bf16": [P, I, P, I, P, I, I, I, I, P],
     "slb_moe_plan_ints": [I, I],
     "slb_moe_plan": [P, I, I, P, P],
     "slb_moe_gate_up_f32": [P, I, P, I, P, I, P, I, I, I, I, I, P],
@@ -236,7 +237,8 @@ _ATTN_KV_SIGNATURES = {
     "slb_attention_kv_mma_value_dim": [],
     "slb_attention_kv_mma_tile_rows": [],
     "slb_attention_kv_mma_status": [I],
-    "slb_attention_kv_mma_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, P],
+    "slb_attention_kv_mma_bf16": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, F, I, P, I, I, P, P, P],
+    "slb_attention_kv_mma_max_splits": [],
 }
 
 
