@@ -98,21 +98,37 @@ def _daferax_rooflines(size, res, peaks) -> Dict[str, object]:
     def tf(flops, us):
         return round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 4)
 
-    att = pk.get("attention_kv_mma") or pk.get("attention_kv")
-    if att:
-        flops = (n_lat * win_pairs * heads * 2 * (2 * rank + rot) + n_att * full_pairs * heads * 2 * 2 * dim)
-        out["daferax_prefill_attention_us_per_layer"] = round(att / LAYERS, 1)
-        out["daferax_prefill_attention_bf16_frac"] = tf(flops, att)
+    # the latent layers run this design's kernel; the grouped layers, whose keys and values are of one
+    # size here, the kernels of the other models (when they are of two sizes: this design's kernel too)
+    lat = pk.get("attention_kv_mma") or pk.get("attention_kv")
+    grp = (pk.get("prefill_attention_tc") or 0) + (pk.get("prefill_attention") or 0)
+    lat_flops = n_lat * win_pairs * heads * 2 * (2 * rank + rot)
+    grp_flops = n_att * full_pairs * heads * 2 * 2 * dim
+    if lat and grp:
+        out["daferax_latent_prefill_attention_us_per_layer"] = round(lat / n_lat, 1)
+        out["daferax_latent_prefill_attention_bf16_frac"] = tf(lat_flops, lat)
+        out["daferax_grouped_prefill_attention_us_per_layer"] = round(grp / n_att, 1)
+        out["daferax_grouped_prefill_attention_bf16_frac"] = tf(grp_flops, grp)
+    elif lat:
+        out["daferax_prefill_attention_us_per_layer"] = round(lat / LAYERS, 1)
+        out["daferax_prefill_attention_bf16_frac"] = tf(lat_flops + grp_flops, lat)
     qatt = (qk.get("prefill_attention_tc") or 0) + (qk.get("prefill_attention") or 0)
     if qatt:
         flops = (LAYERS // 2 * win_pairs + (LAYERS - LAYERS // 2) * full_pairs) * heads * 4 * dim
         out["qwen2_prefill_attention_us_per_layer"] = round(qatt / LAYERS, 1)
         out["qwen2_prefill_attention_bf16_frac"] = tf(flops, qatt)
-    datt = dk.get("attention_kv_mma") or dk.get("attention_kv")
-    if datt:
-        nbytes = 8 * 2 * (n_lat * min(CONTEXT, WINDOW) * (rank + rot) + n_att * CONTEXT * kv * 2 * dim)
-        out["daferax_decode_attention_us_per_layer"] = round(datt / LAYERS, 2)
-        out["daferax_decode_attention_hbm_frac"] = hbm(nbytes, datt)
+    dlat = dk.get("attention_kv_mma") or dk.get("attention_kv")
+    dgrp = dk.get("decode_attention")
+    lat_bytes = 8 * 2 * n_lat * min(CONTEXT, WINDOW) * (rank + rot)
+    grp_bytes = 8 * 2 * n_att * CONTEXT * kv * 2 * dim
+    if dlat and dgrp:
+        out["daferax_latent_decode_attention_us_per_layer"] = round(dlat / n_lat, 2)
+        out["daferax_latent_decode_attention_hbm_frac"] = hbm(lat_bytes, dlat)
+        out["daferax_grouped_decode_attention_us_per_layer"] = round(dgrp / n_att, 2)
+        out["daferax_grouped_decode_attention_hbm_frac"] = hbm(grp_bytes, dgrp)
+    elif dlat:
+        out["daferax_decode_attention_us_per_layer"] = round(dlat / LAYERS, 2)
+        out["daferax_decode_attention_hbm_frac"] = hbm(lat_bytes + grp_bytes, dlat)
     qdatt = qd.get("decode_attention")
     if qdatt:
         nbytes = 8 * 2 * kv * 2 * dim * (LAYERS // 2 * min(CONTEXT, WINDOW) + (LAYERS - LAYERS // 2) * CONTEXT)

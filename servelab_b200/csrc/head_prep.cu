@@ -128,16 +128,17 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
     }
 }
 
-// out = x * sigmoid(gate), element by element, float32 arithmetic.
+// out = x * sigmoid(gate), float32 arithmetic; one gate value per `group` neighbouring elements
+// (1: element by element; a head's size: one number a head).
 template <typename T>
 __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__ x, int ldx,
                                                            const T* __restrict__ gate, int ldg,
-                                                           T* __restrict__ out, int ldo, int N) {
+                                                           T* __restrict__ out, int ldo, int N, int group) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < N; c += blockDim.x) {
-        const float z = to_float(gate[t * ldg + c]);
+        const float z = to_float(gate[t * ldg + c / group]);
         out[t * ldo + c] = from_float<T>(to_float(x[t * ldx + c]) / (1.0f + expf(-z)));
     }
 }
@@ -168,13 +169,15 @@ int slb_head_prep_bf16(const HeadPrepArgs* a, int num_tokens, cudaStream_t st) {
     return launch_head_prep<bf16>(*a, num_tokens, st);
 }
 int slb_sigmoid_gate_f32(const float* x, int ldx, const float* gate, int ldg, float* out, int ldo, int T,
-                         int N, cudaStream_t st) {
+                         int N, int group, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
-    return slb_launch(sigmoid_gate_kernel<float>, dim3(T), dim3(256), 0, st, x, ldx, gate, ldg, out, ldo, N);
+    if (group <= 0) return SLB_ERR_BAD_ARG;
+    return slb_launch(sigmoid_gate_kernel<float>, dim3(T), dim3(256), 0, st, x, ldx, gate, ldg, out, ldo, N, group);
 }
 int slb_sigmoid_gate_bf16(const bf16* x, int ldx, const bf16* gate, int ldg, bf16* out, int ldo, int T,
-                          int N, cudaStream_t st) {
+                          int N, int group, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
-    return slb_launch(sigmoid_gate_kernel<bf16>, dim3(T), dim3(256), 0, st, x, ldx, gate, ldg, out, ldo, N);
+    if (group <= 0) return SLB_ERR_BAD_ARG;
+    return slb_launch(sigmoid_gate_kernel<bf16>, dim3(T), dim3(256), 0, st, x, ldx, gate, ldg, out, ldo, N, group);
 }
 }

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(
                     bi = g;
                 }
             warp_argmax(bv, bi);
-            if (lane == 0) gs[bi] = 2.f;
+            if (lane == 0 && bi < groups) gs[bi] = 2.f;      // (no group found: logits that are no numbers)
             __syncwarp();
         }
     }
@@ -96,10 +96,14 @@ __global__ void __launch_bounds__(128) moe_route_kernel(
             }
         }
         warp_argmax(bv, bi);
+        if (bi >= E) {                                     // nothing left to choose (logits that are no
+            bi = 0;                                        // numbers, as the rows of a padded step may
+            bv = 0.f;                                      // hold): expert 0 with weight 0
+        }
         if (lane == 0) {
             ids[(size_t)t * top + round] = bi;
             weights[(size_t)t * top + round] = bv;
-            s[bi] = -1.f;                                  // taken
+            if (bv > 0.f) s[bi] = -1.f;                    // taken
         }
         chosen_sum += bv;
         __syncwarp();
@@ -415,16 +419,16 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(
 }
 
 // ----------------------------------------------------------------- combine
-template <typename T>
+template <typename T, typename TY>
 __global__ void __launch_bounds__(256) moe_combine_kernel(
-    const float* __restrict__ y, int ldy, const float* __restrict__ weights, const T* __restrict__ shared,
+    const TY* __restrict__ y, int ldy, const float* __restrict__ weights, const T* __restrict__ shared,
     int lds, T* __restrict__ out, int ldo, int top, int N) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) v += weights[(size_t)t * top + k] * y[((size_t)t * top + k) * ldy + c];
+        for (int k = 0; k < top; ++k) v += weights[(size_t)t * top + k] * to_float(y[((size_t)t * top + k) * ldy + c]);
         if (shared != nullptr) v += to_float(shared[(size_t)t * lds + c]);
         out[(size_t)t * ldo + c] = from_float<T>(v);
     }
@@ -527,13 +531,20 @@ int slb_moe_down_bf16(const bf16* act, int lda, const bf16* w_down, int ldw, flo
 int slb_moe_combine_f32(const float* y, int ldy, const float* weights, const float* shared, int lds,
                         float* out, int ldo, int T, int top, int N, cudaStream_t st) {
     if (T <= 0) return 0;
-    return slb_launch(moe_combine_kernel<float>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
+    return slb_launch(moe_combine_kernel<float, float>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
                       out, ldo, top, N);
 }
 int slb_moe_combine_bf16(const float* y, int ldy, const float* weights, const bf16* shared, int lds,
                          bf16* out, int ldo, int T, int top, int N, cudaStream_t st) {
     if (T <= 0) return 0;
-    return slb_launch(moe_combine_kernel<bf16>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
+    return slb_launch(moe_combine_kernel<bf16, float>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st, y, ldy, weights, shared, lds,
                       out, ldo, top, N);
+}
+// the experts' rows in bfloat16 (a library product left them so)
+int slb_moe_combine_bf16_rows(const bf16* y, int ldy, const float* weights, const bf16* shared, int lds,
+                              bf16* out, int ldo, int T, int top, int N, cudaStream_t st) {
+    if (T <= 0) return 0;
+    return slb_launch(moe_combine_kernel<bf16, bf16>, dim3(T, T < 256 ? (N + 255) / 256 : 1), dim3(256), 0, st,
+                      y, ldy, weights, shared, lds, out, ldo, top, N);
 }
 }

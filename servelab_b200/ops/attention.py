@@ -107,6 +107,7 @@ def check_kv_supported(key_dim: int, value_dim: int) -> None:
                             f"1..{KV_MAX_VALUE_DIM} elements, got {key_dim} and {value_dim}")
 
 
+use_equal_size_kernels = True
 use_kv_fast = True         # bfloat16: the tensor-core kernel (off: the plain kernel, its twin)
 KV_FAST_MAX_KEY_DIM, KV_FAST_MAX_VALUE_DIM = 320, 256
 
@@ -130,6 +131,14 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
     rows), causal with an optional window, head h's row times sigmoid(head_gate[t, h]) if given.
     float32, or sizes the tensor-core kernel does not take: the plain kernel."""
     tied = v_cache.data_ptr() == k_cache.data_ptr() and v_row_stride == Dk
+    if (Dk == Dv and not tied and v_row_stride == Dv and q.dtype == torch.bfloat16 and not force_generic
+            and use_equal_size_kernels and K.has_fast_attention(Dk) and Dk in (64, 128)):
+        # keys and values of one size the tcgen05 kernels take: the framework's attention for
+        # equal sizes (tcgen05 prefill, one-launch decode), then the gate in a pass of its own
+        paged_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, Dk, page_size, scale, window)
+        if head_gate is not None:
+            K.sigmoid_gate(out, head_gate, out, group=Dv)
+        return
     if _kv_fast(Dk, Dv, q.dtype) and (tied or v_row_stride == Dv) and q.stride(0) % 8 == 0 \
             and out.stride(0) % 2 == 0:
         K.attention_kv_mma(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,

@@ -883,11 +883,12 @@ def head_prep(proj: torch.Tensor, ctx, block_table: torch.Tensor, page_size: int
     L.check(fn(_ct.byref(a), proj.shape[0], _stream()), "head_prep")
 
 
-def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x * sigmoid(gate), element by element ([T, N] views with any row stride)."""
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, group: int = 1) -> None:
+    """out = x * sigmoid(gate) ([T, N] views with any row stride); ``group``: neighbouring elements
+    that share a gate value (1: element by element; a head's size: one number a head)."""
     fn = getattr(L.core(), "slb_sigmoid_gate_" + _suffix(x.dtype))
     L.check(fn(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), out.data_ptr(), out.stride(0),
-               x.shape[0], x.shape[1], _stream()), "sigmoid_gate")
+               x.shape[0], x.shape[1], int(group), _stream()), "sigmoid_gate")
 
 
 def head_prep_status(reset: bool = False) -> int:
@@ -973,10 +974,20 @@ def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> No
                M, N, Kd, B, a.stride(1), w.stride(0), out.stride(1), _stream()), "gemm_simt_batched")
 
 
+router_vendor_min_tokens = 512
+
+
 def router_logits(x: torch.Tensor, w_f32: torch.Tensor) -> torch.Tensor:
     """float32 logits x . w^T of a float32 router matrix (activations float32 or bfloat16); a
     token's sums run in a fixed order."""
     M, Kd = x.shape
+    if x.dtype == _BF16 and M >= router_vendor_min_tokens:
+        # a large step in the bfloat16 path: the vendor's float32 product (no reduced-precision
+        # mode: torch's default for float32 products) on the widened rows
+        from .profile import mark
+        out = torch.mm(x.float(), w_f32.t())
+        mark("library gemm")
+        return out
     out = torch.empty((M, w_f32.shape[0]), dtype=_F32, device=x.device)
     fn = getattr(L.core(), "slb_router_logits_" + _suffix(x.dtype))
     L.check(fn(x.data_ptr(), x.stride(0), w_f32.data_ptr(), w_f32.stride(0), out.data_ptr(), out.stride(0),
@@ -998,6 +1009,11 @@ def moe_route(logits: torch.Tensor, groups: int, keep: int, top: int, route_scal
     return ids, weights
 
 
+moe_vendor_grouped = True      # bfloat16 steps of many rows: the vendor's grouped product (off: this package's)
+moe_vendor_min_pairs = 1024    # (token, choice) pairs from which it is taken ...
+moe_vendor_min_expert_elements = 1 << 21   # ... for experts of at least this many elements a matrix (measured:
+                                           # width 2,048 x 1,408: 2.8 -> 1.1 ms a 2,048-token step of 4 layers;
+                                           # 1,024 x 512: 0.40 -> 0.62 ms with the copies around it)
 moe_tensor_cores = True        # bfloat16: the experts' products on mma.sync (off: CUDA cores, the twin)
 
 
@@ -1013,6 +1029,31 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     lib = L.core()
     plan = torch.empty(lib.slb_moe_plan_ints(P, E), dtype=torch.int32, device=x.device)
     L.check(lib.slb_moe_plan(ids.data_ptr(), P, E, plan.data_ptr(), _stream()), "moe_plan")
+    if (x.dtype == _BF16 and moe_vendor_grouped and P >= moe_vendor_min_pairs
+            and h * inter >= moe_vendor_min_expert_elements and h % 8 == 0
+            and inter % 8 == 0 and n_out % 8 == 0 and hasattr(torch, "_grouped_mm")):
+        # Large steps: the vendor's grouped product over the rows sorted by expert (the plan's list
+        # and offsets stay on the device), as the dense products of large steps go to the vendor's
+        # GEMM; gathering and scattering rows are copies.
+        from .profile import mark
+        nt = (plan.numel() - 4 * E - 1 - P) // 2
+        ends = plan[E + 1:2 * E + 1]                                   # cumulative row counts
+        order = plan[3 * E + 1 + 2 * nt:3 * E + 1 + 2 * nt + P]        # pairs sorted by expert
+        xs = x.index_select(0, torch.div(order, top, rounding_mode="floor"))
+        gu = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)
+        mark("library grouped gemm")
+        act = torch.empty((P, inter), dtype=x.dtype, device=x.device)
+        swiglu(gu, act, 0)
+        ys = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)
+        mark("library grouped gemm")
+        y = torch.empty_like(ys)
+        y.index_copy_(0, order.long(), ys)
+        out = torch.empty((T, n_out), dtype=x.dtype, device=x.device)
+        L.check(lib.slb_moe_combine_bf16_rows(
+            y.data_ptr(), y.stride(0), weights.data_ptr(), _p(shared),
+            shared.stride(0) if shared is not None else 0, out.data_ptr(), out.stride(0), T, top, n_out,
+            _stream()), "moe_combine")
+        return out
     act = torch.empty((P, inter), dtype=x.dtype, device=x.device)
     sfx = _suffix(x.dtype)
     # bfloat16 with rows of whole 16-byte chunks: the tensor-core products; else CUDA cores

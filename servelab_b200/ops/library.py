@@ -65,8 +65,8 @@ _CORE_SIGNATURES = {
     "slb_head_prep_f32": [P, I, P],
     "slb_head_prep_bf16": [P, I, P],
     "slb_head_prep_status": [I],
-    "slb_sigmoid_gate_f32": [P, I, P, I, P, I, I, I, P],
-    "slb_sigmoid_gate_bf16": [P, I, P, I, P, I, I, I, P],
+    "slb_sigmoid_gate_f32": [P, I, P, I, P, I, I, I, I, P],
+    "slb_sigmoid_gate_bf16": [P, I, P, I, P, I, I, I, I, P],
     "slb_attention_kv_tile_rows": [],
     "slb_attention_kv_status": [I],
     "slb_attention_kv_f32": [P, I, P, P, I, P, I, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, I, P],
@@ -87,6 +87,7 @@ _CORE_SIGNATURES = {
     "slb_moe_down_mma_bf16": [P, I, P, I, P, I, P, I, I, I, I, I, P],
     "slb_moe_combine_f32": [P, I, P, P, I, P, I, I, I, I, P],
     "slb_moe_combine_bf16": [P, I, P, P, I, P, I, I, I, I, P],
+    "slb_moe_combine_bf16_rows": [P, I, P, P, I, P, I, I, I, I, P],
 }
 
 # optional entry points: declared when the library exports them

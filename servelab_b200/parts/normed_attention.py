@@ -58,6 +58,10 @@ class NormedAttention(Mixer):
         self.v_size = spec.num_kv_heads * spec.value_dim
         A.check_kv_supported(spec.head_dim, spec.value_dim)
         A.prepare_kv_attention(spec.head_dim, spec.value_dim, env.dtype)
+        if (spec.head_dim == spec.value_dim and env.dtype == torch.bfloat16 and spec.head_dim in (64, 128)
+                and torch.cuda.is_available()):
+            from ..ops import library
+            library.attention(spec.head_dim)      # the kernels for equal sizes, built now
 
     @classmethod
     def _names(cls, spec, prefix):

@@ -161,7 +161,8 @@ def _attention_case(seed, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, s
             "want": torch.cat(wants), "entries": entries, "row": row}
 
 
-SHAPES = [(4, 2, 48, 32, None), (8, 1, 160, 128, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1)]
+SHAPES = [(4, 2, 48, 32, None), (8, 1, 160, 128, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1),
+          (4, 2, 64, 64, 50), (2, 1, 128, 128, None)]        # (equal sizes: the kernels of the other models)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -232,10 +233,11 @@ def test_router_kernel(shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T", [1, 7, 150])
+@pytest.mark.parametrize("T", [1, 7, 150, 400])
 def test_experts_kernels(dtype, T):
     """The planned products and the weighted sum against the oracle, with experts that get no
-    token and experts that get more than a tile."""
+    token and experts that get more than a tile (400 tokens in bfloat16: the grouped library
+    product over the sorted rows)."""
     from servelab_b200.ops import kernels as K
     E, top, h, inter = 7, 3, 40, 24
     g = torch.Generator().manual_seed(T)
