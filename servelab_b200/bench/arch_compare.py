@@ -51,19 +51,19 @@ def qwen2_config(width, heads, kv, dim, ff, layers=LAYERS) -> dict:
 # experts, groups, kept groups, top, expert size, shared size
 DAFERAX_SIZES = {
     "lite-2048": (2048, 16, 4, 128, 256, 64, 32, 4, 2, 4, 1408, 2816),
-    "small-1024": (1024, 8, 2, 64, 128, 32, 16, 2, 1, 2, 512, 1024),
+    "small-1024": (1024, 8, 2, 64, 192, 32, 16, 2, 1, 2, 512, 1024),
 }
 
 
 def daferax_config(width, heads, kv, dim, rank, rot, experts, groups, keep, top, eff, sff, layers=LAYERS) -> dict:
     mlp = {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
-           "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "scale": 2.5, "top": top}}
+           "router": {"experts": experts, "groups": {"count": groups, "keep": keep}, "scale": 2.0, "top": top}}
     latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": dim, "kv_rank": rank,
               "scale": (dim + rot) ** -0.5, "mask": {"size": WINDOW},
-              "rot": {"base": 500000.0, "dims": rot,
+              "rot": {"base": 250000.0, "dims": rot,
                       "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     attn = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
-            "rot": {"base": 1000000.0, "dims": dim}}
+            "rot": {"base": 2000000.0, "dims": dim}}
     return {"architecture": "Daferax", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-5},
             "layers": [{"type": "latent_attention" if i % 2 == 0 else "attention",
                         "mixer": latent if i % 2 == 0 else attn, "mlp": mlp} for i in range(layers)]}

@@ -152,7 +152,7 @@ def build_all(head_dims=(16, 32, 64, 128)) -> List[str]:
     if os.path.isfile(os.path.join(HERE, "attention_mma.cu")):
         libs += [attention_library(d) for d in head_dims]
     if os.path.isfile(os.path.join(HERE, "attention_kv_mma.cu")):
-        libs += [attention_kv_library(dk, dv) for dk, dv in ((64, 32), (160, 128))]
+        libs += [attention_kv_library(dk, dv) for dk, dv in ((96, 64), (320, 256))]
     return libs
 
 

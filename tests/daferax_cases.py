@@ -58,7 +58,7 @@ V = {"architecture": "Daferax", "vocab": 300, "width": 80, "norm": {"eps": 1e-5}
 # sizes that no 16-byte access fits
 W = {"architecture": "Daferax", "vocab": 97, "width": 50, "norm": {"eps": 1e-5},
      "layers": [layer(attention(3, 3, 10, 6, 4, 900.0, 0.3, window=25), moe(3, 2, 10, None, 1.2, 6)),
-                layer(latent(2, 6, 2, 10, 14, 2000.0, 0.35, window=13), moe(6, 2, 14, (2, 1), 2.5))]}
+                layer(latent(2, 6, 2, 10, 14, 2000.0, 0.35, window=13), moe(6, 2, 14, (2, 1), 2.2))]}
 CASES = {"U": (U, 5, 8), "V": (V, 9, 16), "W": (W, 13, 4)}        # config, seed, page size
 # projections drawn large enough that the softmax of a tiny model is peaked and the router's
 # choice is clear of ties

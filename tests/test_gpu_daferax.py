@@ -161,7 +161,7 @@ def _attention_case(seed, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, s
             "want": torch.cat(wants), "entries": entries, "row": row}
 
 
-SHAPES = [(4, 2, 48, 32, None), (8, 1, 160, 128, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1),
+SHAPES = [(4, 2, 80, 48, None), (5, 1, 112, 96, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1),
           (4, 2, 64, 64, 50), (2, 1, 128, 128, None)]        # (equal sizes: the kernels of the other models)
 
 
@@ -217,17 +217,17 @@ def test_attention_gate_per_head(dtype):
 
 
 # ------------------------------------------------------------------ experts
-@pytest.mark.parametrize("shape", [(6, 3, 2, 2), (8, 1, 1, 1), (64, 8, 4, 6), (12, 3, 2, 3), (5, 1, 1, 5)])
+@pytest.mark.parametrize("shape", [(6, 3, 2, 2), (8, 1, 1, 1), (64, 8, 4, 6), (10, 5, 2, 3), (5, 1, 1, 5)])
 def test_router_kernel(shape):
     from servelab_b200.ops import kernels as K
     E, groups, keep, top = shape
     T = 50
     logits = torch.randn(T, E, generator=torch.Generator().manual_seed(E)) * 2
-    r = {"experts": E, "top": top, "scale": 2.5}
+    r = {"experts": E, "top": top, "scale": 1.7}
     if groups > 1:
         r["groups"] = {"count": groups, "keep": keep}
     want_idx, want_w = plain.route(logits.double(), {"x.router": torch.eye(E, dtype=F64)}, "x.", r)
-    ids, w = K.moe_route(logits.to(DEV), groups, keep, top, 2.5, False)
+    ids, w = K.moe_route(logits.to(DEV), groups, keep, top, 1.7, False)
     assert torch.equal(ids.cpu().long(), want_idx)
     assert (w.cpu().double() - want_w).abs().max() < 1e-6
 
