@@ -1,5 +1,5 @@
 // Plain paged attention for mixers whose keys and values have different sizes: keys of Dk
-// elements (up to 640), values of Dv (up to 512), grouped heads, causal with an optional window,
+// elements (up to 1,088), values of Dv (up to 512), grouped heads, causal with an optional window,
 // any page size, any mix of prompt portions and single tokens.  float32 arithmetic throughout;
 // inputs and outputs float32 or bfloat16.
 //
@@ -23,7 +23,7 @@
 #define AK_BN 32
 #define AK_DC 64
 #define AK_THREADS 256
-#define AK_MAX_DK 640
+#define AK_MAX_DK 1088
 #define AK_MAX_DV 512
 
 SLB_DEFINE_STATUS_WORD(attention_kv_status_word, slb_attention_kv_status)

@@ -22,7 +22,7 @@
 #include "common.cuh"
 
 #define HP_WARPS 4
-#define HP_MAX_D 1024
+#define HP_MAX_D 1152
 
 SLB_DEFINE_STATUS_WORD(head_prep_status_word, slb_head_prep_status)
 

@@ -98,7 +98,7 @@ def talk_attention(ctx, q, k_cache, v_cache, out, table, H, Hkv, D, page_size, s
 
 
 # ------------------------------- attention with keys and values of two sizes
-KV_MAX_KEY_DIM, KV_MAX_VALUE_DIM = 640, 512
+KV_MAX_KEY_DIM, KV_MAX_VALUE_DIM = 1088, 512
 
 
 def check_kv_supported(key_dim: int, value_dim: int) -> None:
