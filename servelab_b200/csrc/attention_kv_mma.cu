@@ -156,17 +156,27 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
             for (int j = 0; j < NT_S; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) sc[j][e] = 0.f;
-#pragma unroll 2
+            // (the fragment loads are issued one k-step ahead of the MMAs that use them: the
+            // instructions keep their program order, so the order is written out here)
+            unsigned af[2][4], bf[2][NT_S / 2][4];
+            ldmatrix_x4(af[0], Qw + (lane & 15) * LDK + (lane >> 4) * 8);
+#pragma unroll
+            for (int jp = 0; jp < NT_S / 2; ++jp)
+                ldmatrix_x4(bf[0][jp], Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + ((lane >> 3) & 1) * 8);
+#pragma unroll
             for (int kk = 0; kk < KSTEPS; ++kk) {
-                unsigned a[4];
-                ldmatrix_x4(a, Qw + (lane & 15) * LDK + kk * 16 + (lane >> 4) * 8);
+                const int cur = kk & 1, nxt = cur ^ 1;
+                if (kk + 1 < KSTEPS) {
+                    ldmatrix_x4(af[nxt], Qw + (lane & 15) * LDK + (kk + 1) * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int jp = 0; jp < NT_S / 2; ++jp)
+                        ldmatrix_x4(bf[nxt][jp], Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + (kk + 1) * 16 +
+                                                     ((lane >> 3) & 1) * 8);
+                }
 #pragma unroll
                 for (int jp = 0; jp < NT_S / 2; ++jp) {
-                    unsigned b[4];
-                    ldmatrix_x4(b, Ks + (jp * 16 + (lane >> 4) * 8 + (lane & 7)) * LDK + kk * 16 +
-                                       ((lane >> 3) & 1) * 8);
-                    mma_bf16(sc[2 * jp], a, b[0], b[1]);
-                    mma_bf16(sc[2 * jp + 1], a, b[2], b[3]);
+                    mma_bf16(sc[2 * jp], af[cur], bf[cur][jp][0], bf[cur][jp][1]);
+                    mma_bf16(sc[2 * jp + 1], af[cur], bf[cur][jp][2], bf[cur][jp][3]);
                 }
             }
             // mask, online softmax (base-2 domain)
@@ -216,13 +226,16 @@ __global__ void __launch_bounds__(NTHREADS) attention_kv_mma_kernel(
                 a[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
                 a[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
                 a[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+                unsigned vf[2][4];
+                ldmatrix_x4_trans(vf[0], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + (lane >> 4) * 8);
 #pragma unroll
                 for (int np = 0; np < NT_O / 2; ++np) {
-                    unsigned b[4];
-                    ldmatrix_x4_trans(b, Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s + np * 16 +
-                                             (lane >> 4) * 8);
-                    mma_bf16(o[2 * np], a, b[0], b[1]);
-                    mma_bf16(o[2 * np + 1], a, b[2], b[3]);
+                    const int cur = np & 1, nxt = cur ^ 1;
+                    if (np + 1 < NT_O / 2)
+                        ldmatrix_x4_trans(vf[nxt], Vs + (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv_s +
+                                                       (np + 1) * 16 + (lane >> 4) * 8);
+                    mma_bf16(o[2 * np], a, vf[cur][0], vf[cur][1]);
+                    mma_bf16(o[2 * np + 1], a, vf[cur][2], vf[cur][3]);
                 }
             }
         }
