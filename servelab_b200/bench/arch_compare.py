@@ -51,7 +51,7 @@ def qwen2_config(width, heads, kv, dim, ff, layers=LAYERS) -> dict:
 # experts, groups, kept groups, top, expert size, shared size
 DAFERAX_SIZES = {
     "lite-2048": (2048, 16, 4, 128, 256, 64, 32, 4, 2, 4, 1408, 2816),
-    "small-1024": (1024, 8, 2, 64, 192, 32, 16, 2, 1, 2, 512, 1024),
+    "small-1024": (1024, 8, 2, 64, 192, 64, 16, 2, 1, 2, 512, 1024),
 }
 
 
@@ -100,7 +100,7 @@ def _daferax_rooflines(size, res, peaks) -> Dict[str, object]:
 
     # the latent layers run this design's kernel; the grouped layers, whose keys and values are of one
     # size here, the kernels of the other models (when they are of two sizes: this design's kernel too)
-    lat = pk.get("attention_kv_mma") or pk.get("attention_kv")
+    lat = (pk.get("attention_kv_tc") or 0) + (pk.get("attention_kv_mma") or 0) + (pk.get("attention_kv") or 0)
     grp = (pk.get("prefill_attention_tc") or 0) + (pk.get("prefill_attention") or 0)
     lat_flops = n_lat * win_pairs * heads * 2 * (2 * rank + rot)
     grp_flops = n_att * full_pairs * heads * 2 * 2 * dim

@@ -143,7 +143,7 @@ def attention_library(head_dim: int) -> str:
 
 def attention_kv_library(key_dim: int, value_dim: int) -> str:
     """The tensor-core attention for keys and values of two sizes, specialised for one pair."""
-    return ensure_library(f"slb_attn_k{key_dim}v{value_dim}", ["attention_kv_mma.cu"],
+    return ensure_library(f"slb_attn_k{key_dim}v{value_dim}", ["attention_kv_mma.cu", "attention_kv_tc.cu"],
                           {"SLB_KEY_DIM": key_dim, "SLB_VALUE_DIM": value_dim})
 
 
@@ -152,7 +152,7 @@ def build_all(head_dims=(16, 32, 64, 128)) -> List[str]:
     if os.path.isfile(os.path.join(HERE, "attention_mma.cu")):
         libs += [attention_library(d) for d in head_dims]
     if os.path.isfile(os.path.join(HERE, "attention_kv_mma.cu")):
-        libs += [attention_kv_library(dk, dv) for dk, dv in ((96, 64), (320, 256))]
+        libs += [attention_kv_library(dk, dv) for dk, dv in ((96, 64), (320, 256), (128, 64))]
     return libs
 
 

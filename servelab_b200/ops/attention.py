@@ -141,6 +141,11 @@ def kv_attention(ctx, q, k_cache, v_cache, v_row_stride, out, table, H, Hkv, Dk,
         return
     if _kv_fast(Dk, Dv, q.dtype) and (tied or v_row_stride == Dv) and q.stride(0) % 8 == 0 \
             and out.stride(0) % 2 == 0:
+        if (not ctx.decode_only and out.stride(0) % 8 == 0
+                and K.attention_kv_tc_takes(Dk, Dv, page_size, H // Hkv, tied)):
+            K.attention_kv_tc(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
+                              window, head_gate)
+            return
         K.attention_kv_mma(ctx, q, k_cache, v_cache, tied, out, table, H, Hkv, Dk, Dv, page_size, scale,
                            window, head_gate)
         return

@@ -959,6 +959,35 @@ def attention_kv_mma(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num
 attention_kv_split = True      # (off: one block a request and kv head, the twin)
 
 
+attention_kv_use_tc = True     # steps with prompt portions: the tcgen05 kernel where it takes the sizes
+
+
+def attention_kv_tc_takes(k_dim: int, v_dim: int, page_size: int, group: int, tied: bool) -> bool:
+    return bool(attention_kv_use_tc and L.attention_kv(k_dim, v_dim).slb_attention_kv_tc_supported(
+        page_size, group, 1 if tied else 0))
+
+
+def attention_kv_tc(ctx, q, k_cache, v_cache, tied: bool, out, block_table, num_heads: int,
+                    num_kv_heads: int, k_dim: int, v_dim: int, page_size: int, scale: float, window: int,
+                    head_gate: Optional[torch.Tensor] = None) -> None:
+    """The tcgen05 kernel (bfloat16; key and value sizes multiples of 64; steps with prompt
+    portions): 128 flattened rows a block, accumulators in tensor memory."""
+    lib = L.attention_kv(k_dim, v_dim)
+    group = num_heads // num_kv_heads
+    tile_seq, tile_row0, n = ctx.attention_tiles(group, lib.slb_attention_kv_tc_tile_rows(group))
+    L.check(lib.slb_attention_kv_tc_bf16(
+        q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), 1 if tied else 0, out.data_ptr(),
+        out.stride(0), block_table.data_ptr(), block_table.shape[1], ctx.cu_q.data_ptr(),
+        ctx.ctx_len.data_ptr(), tile_seq.data_ptr(), tile_row0.data_ptr(), n, num_heads, num_kv_heads,
+        page_size, k_cache.shape[0], float(scale), int(window), _p(head_gate),
+        head_gate.stride(0) if head_gate is not None else 0, _stream()), "attention_kv_tc")
+
+
+def attention_kv_tc_status(k_dim: int, v_dim: int, reset: bool = False) -> int:
+    """0, or the code of the first bounded wait of the tcgen05 kernel that gave up."""
+    return L.attention_kv(k_dim, v_dim).slb_attention_kv_tc_status(1 if reset else 0)
+
+
 def attention_kv_mma_status(k_dim: int, v_dim: int, reset: bool = False) -> int:
     return L.attention_kv(k_dim, v_dim).slb_attention_kv_mma_status(1 if reset else 0)
 

@@ -163,7 +163,8 @@ def _attention_case(seed, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, s
 
 SHAPES = [(4, 2, 80, 48, None), (5, 1, 112, 96, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1),
           (4, 2, 64, 64, 50), (2, 1, 128, 128, None),        # (equal sizes: the kernels of the other models)
-          (4, 1, 224, 192, 40), (2, 2, 208, 64, None)]       # (keys beyond 192 elements: tiles of 32 keys)
+          (4, 1, 224, 192, 40), (2, 2, 208, 64, None),       # (keys beyond 192 elements: tiles of 32 keys)
+          (4, 1, 128, 64, 40), (2, 2, 128, 64, None), (16, 1, 320, 256, 100), (4, 2, 192, 128, 33)]   # (multiples of 64: tcgen05)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -192,6 +193,9 @@ def test_attention_with_keys_and_values_of_two_sizes(dtype, spike, shape, decode
     got = out.cpu().double()
     tol = 1e-4 if dtype == torch.float32 else 6e-2
     assert (got - case["want"]).abs().max() < tol * max(1.0, float(case["want"].abs().max()))
+    if dtype == torch.bfloat16 and Dk % 64 == 0 and Dv % 64 == 0 and Dk != Dv:
+        from servelab_b200.ops import kernels as K
+        assert K.attention_kv_tc_status(Dk, Dv) == 0 and K.attention_kv_mma_status(Dk, Dv) == 0
     if dtype == torch.bfloat16:
         A.force_generic = True                    # the plain kernel, the twin of the fast ones
         try:
