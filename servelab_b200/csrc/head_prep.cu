@@ -18,7 +18,8 @@
 // The same kernel serves a grouped-query attention (queries and keys normed over the whole head
 // and rotated from element 0) and a latent attention (one "key" of latent + rotated part: norm
 // over the latent, rotation of the rest; queries rotated from `rot_off` on, not normed).
-// One block a token, one warp a vector at a time; float32 arithmetic, angles in float32.
+// One block a token (and group of vectors), one warp a vector at a time; the token's sines and
+// cosines are formed once a block; float32 arithmetic, angles in float32.
 #include "common.cuh"
 
 #define HP_WARPS 4
@@ -48,8 +49,17 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int maxd = max(max(a.Dq, a.Dk), a.Dv);
     float* buf = hp_smem + (size_t)warp * maxd;
+    float* cs_tab = hp_smem + (size_t)HP_WARPS * maxd;     // cos and sin of the token's angles, once a block
+    float* sn_tab = cs_tab + a.rot_dims / 2;
     const T* row = reinterpret_cast<const T*>(a.proj) + (size_t)t * a.ld;
     const int pos = a.positions[t];
+    for (int i = threadIdx.x; i < a.rot_dims / 2; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * a.freq[i], &sn, &cs);
+        cs_tab[i] = cs * a.rot_mag;
+        sn_tab[i] = sn * a.rot_mag;
+    }
+    __syncthreads();
     // where this token's key and value go
     long long slot = -1;
     if (a.k_cache != nullptr || a.v_cache != nullptr) {
@@ -111,11 +121,7 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
             }
             if (rotate) {
                 for (int i = lane; i < a.rot_dims / 2; i += 32) {
-                    const float ang = (float)pos * a.freq[i];
-                    float sn, cs;
-                    sincosf(ang, &sn, &cs);
-                    sn *= a.rot_mag;
-                    cs *= a.rot_mag;
+                    const float sn = sn_tab[i], cs = cs_tab[i];
                     const float x = buf[rot_off + 2 * i], y = buf[rot_off + 2 * i + 1];
                     buf[rot_off + 2 * i] = x * cs - y * sn;
                     buf[rot_off + 2 * i + 1] = y * cs + x * sn;
@@ -155,7 +161,7 @@ static int launch_head_prep(const HeadPrepArgs& a, int num_tokens, cudaStream_t 
     if (a.q_norm_dims > a.Dq || a.k_norm_dims > a.Dk || a.q_skip < 0 || a.q_skip > a.Dq) return SLB_ERR_BAD_ARG;
     if ((a.k_cache != nullptr || a.v_cache != nullptr) && (a.block_table == nullptr || a.page_size <= 0))
         return SLB_ERR_BAD_ARG;
-    const size_t smem = (size_t)HP_WARPS * maxd * sizeof(float);
+    const size_t smem = ((size_t)HP_WARPS * maxd + a.rot_dims) * sizeof(float);
     const int units = a.H + a.G + (a.v_off >= 0 ? a.G : 0);
     const int gy = num_tokens < 512 ? (units + HP_WARPS - 1) / HP_WARPS : 1;
     return slb_launch(head_prep_kernel<T>, dim3(num_tokens, gy), dim3(HP_WARPS * 32), smem, st, a);

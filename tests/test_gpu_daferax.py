@@ -264,7 +264,7 @@ def test_experts_kernels(dtype, T):
 
 # ------------------------------------------------------------ whole models
 LENGTHS = [70, 45, 190, 33, 2, 1, 58]
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+TOL = {"float32": 5e-5, "bfloat16": 3e-2}       # of the largest logit (float32: peaked softmaxes amplify rounding)
 
 
 @pytest.fixture(scope="module", params=["U", "V", "W"])
