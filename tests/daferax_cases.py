@@ -59,7 +59,13 @@ V = {"architecture": "Daferax", "vocab": 300, "width": 80, "norm": {"eps": 1e-5}
 W = {"architecture": "Daferax", "vocab": 97, "width": 50, "norm": {"eps": 1e-5},
      "layers": [layer(attention(3, 3, 10, 6, 4, 900.0, 0.3, window=25), moe(3, 2, 10, None, 1.2, 6)),
                 layer(latent(2, 6, 2, 10, 14, 2000.0, 0.35, window=13), moe(6, 2, 14, (2, 1), 2.2))]}
-CASES = {"U": (U, 5, 8), "V": (V, 9, 16), "W": (W, 13, 4)}        # config, seed, page size
+# key and value sizes that are multiples of 64 and differ: the tcgen05 attention for two sizes, with the
+# values inside the key rows (latent: 64 + 64 against 64) and apart from them (128 against 64)
+X = {"architecture": "Daferax", "vocab": 150, "width": 64, "norm": {"eps": 1e-5},
+     "layers": [layer(latent(2, 16, 64, 16, 64, 3000.0, 0.1, window=40,
+                             scaling={"factor": 2.0, "original": 48, "fast": 6.0, "slow": 1.0}), moe(4, 2, 16, None, 1.3)),
+                layer(attention(2, 1, 128, 64, 64, 40000.0, 0.08), {"kind": "dense", "ff": 48})]}
+CASES = {"U": (U, 5, 8), "V": (V, 9, 16), "W": (W, 13, 4), "X": (X, 17, 16)}        # config, seed, page size
 # projections drawn large enough that the softmax of a tiny model is peaked and the router's
 # choice is clear of ties
 STD_OF = {"embed": 0.5, ".mix.q": 0.3, ".mix.k": 0.3, ".mix.dkv": 0.3, ".mix.uk": 0.3, ".router": 0.4}
