@@ -164,7 +164,8 @@ def _attention_case(seed, Hq, G, Dk, Dv, window, ctxs, qlens, ps, dtype, tied, s
 SHAPES = [(4, 2, 80, 48, None), (5, 1, 112, 96, 40), (3, 3, 10, 6, 9), (2, 2, 32, 64, 33), (6, 1, 72, 64, 1),
           (4, 2, 64, 64, 50), (2, 1, 128, 128, None),        # (equal sizes: the kernels of the other models)
           (4, 1, 224, 192, 40), (2, 2, 208, 64, None),       # (keys beyond 192 elements: tiles of 32 keys)
-          (4, 1, 128, 64, 40), (2, 2, 128, 64, None), (16, 1, 320, 256, 100), (4, 2, 192, 128, 33)]   # (multiples of 64: tcgen05)
+          (4, 1, 128, 64, 40), (2, 2, 128, 64, None), (16, 1, 320, 256, 100), (4, 2, 192, 128, 33),   # (multiples of 64: tcgen05)
+          (2, 2, 32, 32, 20), (3, 1, 96, 96, None)]           # (equal sizes the other models' kernels do not take)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
